@@ -1,7 +1,10 @@
 """Architecture descriptions.  Importing the package registers them."""
+from ..config.boketar import BoketarConfig
 from ..config.falcon_h1 import FalconH1Config
 from ..config.registry import register_architecture
-from . import falcon_h1
+from . import boketar, falcon_h1
 
 register_architecture("falcon_h1", FalconH1Config.from_dict, falcon_h1.model_spec,
                       aliases=("FalconH1ForCausalLM",))
+register_architecture("Boketar", BoketarConfig.from_dict, boketar.model_spec, aliases=("boketar",),
+                      reads_tensor_shapes=True)

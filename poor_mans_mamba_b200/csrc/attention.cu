@@ -11,6 +11,7 @@
 // fallback of the bfloat16 path; the tensor-core kernels cover the long cases.
 //
 //   sc[s] = (q.K[s]) * scale;  p = exp(sc - max);  o = sum p V / sum p
+// With ``sink`` (one float per query head) the denominator also holds exp(sink[h] - max).
 // (reference src/ops/gpu/attention.cu:44-105).
 #include "common.cuh"
 #include <math_constants.h>
@@ -55,7 +56,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
                            const int* __restrict__ positions, const int* __restrict__ seq_of,
                            S* __restrict__ out, float* __restrict__ part_o,
                            float* __restrict__ part_ml, float scale, int window, int split_len,
-                           int n_splits, int page_size, int Hq, int Hkv, int Dh) {
+                           int n_splits, int page_size, int Hq, int Hkv, int Dh,
+                           const float* __restrict__ sink) {
   extern __shared__ float qs[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -110,6 +112,16 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
     m = m_new;
   }
 
+  if (sink && z == 0) {
+    // a score without key or value, counted once: it joins the first key range (which may be empty)
+    const float sk = sink[hq];
+    const float m_new = fmaxf(m, sk);
+    const float corr = expf(m - m_new);
+    l = l * corr + expf(sk - m_new);
+#pragma unroll
+    for (int i = 0; i < kAttnMaxAcc; ++i) acc[i] *= corr;
+    m = m_new;
+  }
   if (n_splits == 1) {
     const float inv = 1.f / l;
 #pragma unroll
@@ -138,7 +150,7 @@ PMM_EXPORT int pmm_paged_attention(const void* q, const void* pool, const int* b
                                    int max_blocks, const int* positions, const int* seq_of,
                                    void* out, float* part_o, float* part_ml, float scale, int window,
                                    int split_len, int n_splits, int page_size, int T, int Hq,
-                                   int Hkv, int Dh, int dtype, cudaStream_t stream) {
+                                   int Hkv, int Dh, int dtype, const float* sink, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (Dh <= 0 || Dh % 16 || Dh > 32 * pmm::kAttnMaxAcc) return PMM_ERR_BAD_ARGUMENT;
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || page_size <= 0 || n_splits < 1 || n_splits > 65535)
@@ -153,7 +165,7 @@ PMM_EXPORT int pmm_paged_attention(const void* q, const void* pool, const int* b
     pmm::paged_attention_kernel<S><<<grid, pmm::kAttnWarps * 32, smem, stream>>>(
         static_cast<const S*>(q), static_cast<const S*>(pool), block_table, max_blocks, positions,
         seq_of, static_cast<S*>(out), part_o, part_ml, scale, window, split_len, n_splits,
-        page_size, Hq, Hkv, Dh);
+        page_size, Hq, Hkv, Dh, sink);
   });
   return pmm::launch_status();
 }

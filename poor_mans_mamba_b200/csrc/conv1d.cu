@@ -6,7 +6,7 @@
 // input is the affine image v = raw*pre_scale[c] + pre_bias[c] of a column slice of the
 // input projection, so no separate "split and scale" pass exists.
 //
-//   a = bias[c] + sum_{k<K-1} w[c,k]*v[j-(K-1)+k] + w[c,K-1]*v[j];  y = silu(a)
+//   a = bias[c] + sum_{k<K-1} w[c,k]*v[j-(K-1)+k] + w[c,K-1]*v[j];  y = silu(a)  (y = a when act is 0)
 // (reference src/ops/gpu/conv.cu:3-26, which walks tokens serially per channel).
 //
 // conv1d_fwd reads the window, conv1d_window_update writes it afterwards (separate
@@ -23,7 +23,7 @@ __global__ void conv1d_fwd_kernel(const S* __restrict__ x, long long ldx,
                                   const float* __restrict__ bias, const float* __restrict__ window,
                                   const int* __restrict__ seq_of, const int* __restrict__ cu,
                                   const int* __restrict__ slots, S* __restrict__ y, int T, int C,
-                                  int K) {
+                                  int K, int act) {
   pdl_launch_dependents();
   pdl_wait();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -47,7 +47,7 @@ __global__ void conv1d_fwd_kernel(const S* __restrict__ x, long long ldx,
     }
     acc += wrow[k] * v;
   }
-  stf(y + static_cast<size_t>(t) * C + c, silu_f(acc));
+  stf(y + static_cast<size_t>(t) * C + c, act ? silu_f(acc) : acc);
 }
 
 template <typename S>
@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(128)
                           const float* __restrict__ pre_bias, const float* __restrict__ w_t,
                           const float* __restrict__ bias, const float* __restrict__ window,
                           const int* __restrict__ seq_of, const int* __restrict__ cu,
-                          const int* __restrict__ slots, __nv_bfloat16* __restrict__ y, int T, int C) {
+                          const int* __restrict__ slots, __nv_bfloat16* __restrict__ y, int T, int C, int act) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int L = K - 1;
@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
         for (int k = 0; k < L; ++k) acc += wk[e][k] * hist[k][e];
         acc += wk[e][L] * v[e];
-        a[e] = silu_fast(acc);  // rounded to bfloat16 next
+        a[e] = act ? silu_fast(acc) : acc;  // rounded to bfloat16 next
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(a[2 * e], a[2 * e + 1]);
@@ -199,7 +199,7 @@ __global__ void conv1d_decode_kernel(const S* __restrict__ x, long long ldx,
                                      const float* __restrict__ pre_bias, const float* __restrict__ w,
                                      const float* __restrict__ bias, float* __restrict__ window,
                                      const int* __restrict__ slots, S* __restrict__ y, int n_seq,
-                                     int C, int K) {
+                                     int C, int K, int act) {
   pdl_launch_dependents();
   pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -217,8 +217,8 @@ __global__ void conv1d_decode_kernel(const S* __restrict__ x, long long ldx,
     if (k > 0) win[static_cast<size_t>(k - 1) * C + c] = v;
   }
   acc += wrow[left] * v_new;
-  win[static_cast<size_t>(left - 1) * C + c] = v_new;
-  stf(y + static_cast<size_t>(s) * C + c, silu_f(acc));
+  if (left > 0) win[static_cast<size_t>(left - 1) * C + c] = v_new;
+  stf(y + static_cast<size_t>(s) * C + c, act ? silu_f(acc) : acc);
 }
 
 }  // namespace pmm
@@ -227,25 +227,25 @@ __global__ void conv1d_decode_kernel(const S* __restrict__ x, long long ldx,
 PMM_EXPORT int pmm_conv1d_fwd(const void* x, long long ldx, const float* pre_scale,
                               const float* pre_bias, const float* w, const float* w_t, const float* bias,
                               const float* window, const int* seq_of, const int* cu,
-                              const int* slots, void* y, int T, int C, int K, int dtype,
+                              const int* slots, void* y, int T, int C, int K, int dtype, int act,
                               cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (K < 2 || C <= 0 || (C + 127) / 128 > 65535) return PMM_ERR_BAD_ARGUMENT;
+  if (K < 1 || C <= 0 || (C + 127) / 128 > 65535) return PMM_ERR_BAD_ARGUMENT;
   auto aligned16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   if (dtype == PMM_DTYPE_BF16 && w_t && K >= 2 && K <= 4 && C % 8 == 0 && ldx % 8 == 0 && aligned16(x) &&
       aligned16(y) && aligned16(w_t) && aligned16(pre_scale) && aligned16(pre_bias) && aligned16(bias)) {
     dim3 vgrid((T + pmm::kConvStrip - 1) / pmm::kConvStrip, (C / 8 + 127) / 128);
     const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
     __nv_bfloat16* yb = static_cast<__nv_bfloat16*>(y);
-    if (K == 2) pmm::launch_pdl(pmm::conv1d_fwd_vec_kernel<2>, vgrid, dim3(128), 0, stream, xb, ldx, pre_scale, pre_bias, w_t, bias, window, seq_of, cu, slots, yb, T, C);
-    if (K == 3) pmm::launch_pdl(pmm::conv1d_fwd_vec_kernel<3>, vgrid, dim3(128), 0, stream, xb, ldx, pre_scale, pre_bias, w_t, bias, window, seq_of, cu, slots, yb, T, C);
-    if (K == 4) pmm::launch_pdl(pmm::conv1d_fwd_vec_kernel<4>, vgrid, dim3(128), 0, stream, xb, ldx, pre_scale, pre_bias, w_t, bias, window, seq_of, cu, slots, yb, T, C);
+    if (K == 2) pmm::launch_pdl(pmm::conv1d_fwd_vec_kernel<2>, vgrid, dim3(128), 0, stream, xb, ldx, pre_scale, pre_bias, w_t, bias, window, seq_of, cu, slots, yb, T, C, act);
+    if (K == 3) pmm::launch_pdl(pmm::conv1d_fwd_vec_kernel<3>, vgrid, dim3(128), 0, stream, xb, ldx, pre_scale, pre_bias, w_t, bias, window, seq_of, cu, slots, yb, T, C, act);
+    if (K == 4) pmm::launch_pdl(pmm::conv1d_fwd_vec_kernel<4>, vgrid, dim3(128), 0, stream, xb, ldx, pre_scale, pre_bias, w_t, bias, window, seq_of, cu, slots, yb, T, C, act);
     return pmm::launch_status();
   }
   dim3 grid(T, (C + 127) / 128);
   PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::conv1d_fwd_kernel<S>, grid, dim3(128), 0, stream,
                                    static_cast<const S*>(x), ldx, pre_scale, pre_bias, w, bias,
-                                   window, seq_of, cu, slots, static_cast<S*>(y), T, C, K));
+                                   window, seq_of, cu, slots, static_cast<S*>(y), T, C, K, act));
   return pmm::launch_status();
 }
 
@@ -253,8 +253,8 @@ PMM_EXPORT int pmm_conv1d_window_update(const void* x, long long ldx, const floa
                                         const float* pre_bias, float* window, const int* cu,
                                         const int* slots, int n_seq, int C, int K, int dtype,
                                         cudaStream_t stream) {
-  if (n_seq <= 0) return 0;
-  if (K < 2 || C <= 0 || n_seq > 65535) return PMM_ERR_BAD_ARGUMENT;
+  if (n_seq <= 0 || K == 1) return 0;
+  if (K < 1 || C <= 0 || n_seq > 65535) return PMM_ERR_BAD_ARGUMENT;
   dim3 grid((C + 127) / 128, n_seq);
   PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::conv1d_window_update_kernel<S>, grid, dim3(128), 0, stream,
                                    static_cast<const S*>(x), ldx, pre_scale, pre_bias, window, cu,
@@ -265,12 +265,12 @@ PMM_EXPORT int pmm_conv1d_window_update(const void* x, long long ldx, const floa
 PMM_EXPORT int pmm_conv1d_decode(const void* x, long long ldx, const float* pre_scale,
                                  const float* pre_bias, const float* w, const float* bias,
                                  float* window, const int* slots, void* y, int n_seq, int C, int K,
-                                 int dtype, cudaStream_t stream) {
+                                 int dtype, int act, cudaStream_t stream) {
   if (n_seq <= 0) return 0;
-  if (K < 2 || C <= 0 || n_seq > 65535) return PMM_ERR_BAD_ARGUMENT;
+  if (K < 1 || C <= 0 || n_seq > 65535) return PMM_ERR_BAD_ARGUMENT;
   dim3 grid((C + 127) / 128, n_seq);
   PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::conv1d_decode_kernel<S>, grid, dim3(128), 0, stream,
                                                static_cast<const S*>(x), ldx, pre_scale, pre_bias, w, bias,
-                                               window, slots, static_cast<S*>(y), n_seq, C, K));
+                                               window, slots, static_cast<S*>(y), n_seq, C, K, act));
   return pmm::launch_status();
 }

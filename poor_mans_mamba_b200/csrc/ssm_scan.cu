@@ -198,11 +198,12 @@ __global__ void __launch_bounds__(kScanRows* kScanTpr)
 //   no weight:            out = y * silu(z)
 //   weight, gate first:   out = rmsnorm_group(y * silu(z)) * w
 //   weight, norm first:   out = rmsnorm_group(y) * w * silu(z)
-template <typename S>
-__global__ void gated_norm_kernel(const S* __restrict__ y, const S* __restrict__ z_raw,
+// (gate_sigmoid: sigmoid(z) in place of silu(z))
+template <typename S, typename Y>
+__global__ void gated_norm_kernel(const Y* __restrict__ y, const S* __restrict__ z_raw,
                                   long long ld_z, float z_scale, const float* __restrict__ z_bias,
                                   const float* __restrict__ w, float eps, int norm_before_gate,
-                                  S* __restrict__ out, int I, int group_width) {
+                                  S* __restrict__ out, int I, int group_width, int gate_sigmoid) {
   extern __shared__ float buf[];
   __shared__ float red[32];
   pdl_launch_dependents();
@@ -214,7 +215,7 @@ __global__ void gated_norm_kernel(const S* __restrict__ y, const S* __restrict__
     const int c = c0 + i;
     const float yv = ldf(y + static_cast<size_t>(t) * I + c);
     const float zv = ldf(z_raw + static_cast<long long>(t) * ld_z + c) * z_scale + (z_bias ? z_bias[c] : 0.f);
-    const float gate = silu_f(zv);
+    const float gate = gate_sigmoid ? 1.f / (1.f + expf(-zv)) : silu_f(zv);
     float v;
     if (!w) {
       stf(out + static_cast<size_t>(t) * I + c, yv * gate);
@@ -302,7 +303,7 @@ PMM_EXPORT int pmm_ssm_scan_seq(const void* xbc, int ld_xbc, const void* dt_raw,
 
 PMM_EXPORT int pmm_gated_norm(const void* y, const void* z_raw, long long ld_z, float z_scale,
                               const float* z_bias, const float* w, float eps, int norm_before_gate,
-                              void* out, int T, int I, int n_groups, int dtype,
+                              void* out, int T, int I, int n_groups, int dtype, int y_f32, int gate_sigmoid,
                               cudaStream_t stream) {
   if (T <= 0) return 0;
   if (n_groups <= 0 || I % n_groups || n_groups > 65535) return PMM_ERR_BAD_ARGUMENT;
@@ -310,15 +311,22 @@ PMM_EXPORT int pmm_gated_norm(const void* y, const void* z_raw, long long ld_z, 
   const size_t smem = w ? static_cast<size_t>(gw) * sizeof(float) * (norm_before_gate ? 2 : 1) : 0;
   if (smem > 200 * 1024) return PMM_ERR_BAD_ARGUMENT;
   dim3 grid(T, n_groups);
+#define PMM_GATED_NORM_CASE(Y)                                                                                     \
+  do {                                                                                                             \
+    auto kern = pmm::gated_norm_kernel<S, Y>;                                                                      \
+    if (smem > 48 * 1024) {                                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                      \
+                                           static_cast<int>(smem));                                                \
+      if (e != cudaSuccess) return static_cast<int>(e);                                                            \
+    }                                                                                                              \
+    pmm::launch_pdl(kern, grid, dim3(256), smem, stream, static_cast<const Y*>(y), static_cast<const S*>(z_raw),   \
+                    ld_z, z_scale, z_bias, w, eps, norm_before_gate, static_cast<S*>(out), I, gw, gate_sigmoid);   \
+  } while (0)
+  // y_f32: the rows to norm are floats whatever the storage type (a recurrence's output)
   PMM_DISPATCH_DTYPE(dtype, S, {
-    auto kern = pmm::gated_norm_kernel<S>;
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(smem));
-      if (e != cudaSuccess) return static_cast<int>(e);
-    }
-    pmm::launch_pdl(kern, grid, dim3(256), smem, stream, static_cast<const S*>(y), static_cast<const S*>(z_raw), ld_z,
-                    z_scale, z_bias, w, eps, norm_before_gate, static_cast<S*>(out), I, gw);
+    if (y_f32) PMM_GATED_NORM_CASE(float);
+    else PMM_GATED_NORM_CASE(S);
   });
+#undef PMM_GATED_NORM_CASE
   return pmm::launch_status();
 }

@@ -53,13 +53,19 @@ class Model:
 
     # ------------------------------------------------------------------ tensors
     def named_parts(self) -> List[Tuple[str, Part]]:
-        """(name prefix, part) for every part that owns tensors."""
+        """(name prefix, part) for every part that owns tensors.  A tensor's full name is the
+        prefix, a dot and the tensor's name within its part; a part's tensor without a name of its
+        own (a norm stored as ``<layer>.norm1``) is the prefix itself (`_full_name`)."""
         out: List[Tuple[str, Part]] = []
         for layer in self.layers:
             for part in layer.parts():
-                out.append((f"{layer.prefix}{part.name}.", part))
-        out.append((f"{self.spec.final_norm.name}.", self.final_norm))
+                out.append((f"{layer.prefix}{part.name}", part))
+        out.append((self.spec.final_norm.name, self.final_norm))
         return out
+
+    @staticmethod
+    def _full_name(prefix: str, name: str) -> str:
+        return f"{prefix}.{name}" if name else prefix
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         specs: Dict[str, ParamSpec] = {
@@ -70,13 +76,13 @@ class Model:
             specs[self.spec.head_name] = ParamSpec(self.spec.head_name, (self.vocab_size, self.hidden_size))
         for prefix, part in self.named_parts():
             for ps in part.param_specs():
-                specs[prefix + ps.name] = ps
+                specs[self._full_name(prefix, ps.name)] = ps
         return specs
 
     def ignored_names(self) -> List[str]:
         names: List[str] = []
         for prefix, part in self.named_parts():
-            names += [prefix + n for n in getattr(part, "ignored_names", lambda: [])()]
+            names += [self._full_name(prefix, n) for n in getattr(part, "ignored_names", lambda: [])()]
         return names
 
     def bind(self, tensors: Dict[str, Tensor], dtype: torch.dtype, device: torch.device) -> None:
@@ -85,7 +91,7 @@ class Model:
         self.embedding = tensors[self.spec.embedding_name]
         self.head = self.embedding if self.spec.head_name is None else tensors[self.spec.head_name]
         for prefix, part in self.named_parts():
-            part.bind({ps.name: tensors[prefix + ps.name] for ps in part.param_specs()})
+            part.bind({ps.name: tensors[self._full_name(prefix, ps.name)] for ps in part.param_specs()})
         for layer in self.layers:
             layer.finalize(dtype, self.device)
         self.final_norm.finalize(dtype, self.device)
@@ -115,7 +121,7 @@ class Model:
         T, D = ctx.n_tokens, self.hidden_size
         h = ws.alloc((T, D), torch.float32)
         K.embed(h, self.embedding, ctx.tokens, self.spec.embedding_multiplier)
-        stream = ResidualStream(h, ctx, self._branch_buffers)
+        stream = ResidualStream(h, ctx, self._branch_buffers, lanes=self.spec.residual_lanes)
         order = self.spec.order
         # Fetching the next layer's weights beside a layer's products pays where the mixers' phase is
         # long enough to cover it and the products still wait for their weights: measured on the 0.5B
@@ -132,7 +138,8 @@ class Model:
         ctx.fetch_ahead = None
         self._join(ctx, h.device)
         if ctx.n_rows == 0:
-            stream.flush()
+            if stream.lanes is None:
+                stream.flush()
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=h.device)
         normed = stream.normed(self.final_norm, rows=ctx.logit_rows)
         return self._head(normed, ctx)

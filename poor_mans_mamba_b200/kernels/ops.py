@@ -34,11 +34,11 @@ _SIGNATURES = {
     "pmm_scale_f32": [c_void_p, c_float, c_longlong, c_void_p],
     "pmm_cast_scale": [c_void_p, c_void_p, c_float, c_longlong, c_int, c_void_p],
     "pmm_conv1d_fwd": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_conv1d_window_update": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_conv1d_decode": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_ssm_scan_seq": [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p, c_void_p,
                          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                          c_int, c_void_p, c_longlong, c_float, c_void_p, c_int, c_int, c_void_p],
@@ -51,7 +51,7 @@ _SIGNATURES = {
                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                    c_longlong, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "pmm_gated_norm": [c_void_p, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_float, c_int,
-                       c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_qkv_rope_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
                            c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                            c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -60,7 +60,19 @@ _SIGNATURES = {
                      c_int, c_int, c_void_p],
     "pmm_paged_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
-                            c_int, c_int, c_int, c_void_p],
+                            c_int, c_int, c_int, c_void_p, c_void_p],
+    "pmm_hc_mix_norm": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                        c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "pmm_normed_sum": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_int, c_int, c_int, c_int,
+                       c_void_p],
+    "pmm_rope_pairs_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                             c_int, c_int, c_int, c_void_p],
+    "pmm_delta_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
+                       c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                       c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
+    "pmm_decay_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_flash_supported": [c_int, c_int, c_int],
     "pmm_flash_paged_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -405,6 +417,8 @@ def cast_scale(out: Tensor, src: Tensor, s: float) -> None:
 
 def _conv_common(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], window: Tensor, K: int):
     C = x.shape[1]
+    if K < 1:
+        raise KernelError("conv1d: at least one tap")
     _f32vec(pre_scale, C, "conv1d: pre_scale")
     _f32vec(pre_bias, C, "conv1d: pre_bias")
     if not (window.dtype == torch.float32 and window.is_contiguous() and window.dim() == 3
@@ -415,8 +429,8 @@ def _conv_common(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], windo
 
 def conv1d_fwd(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], weight: Tensor,
                bias: Optional[Tensor], window: Tensor, seq_of: Tensor, cu: Tensor, slots: Tensor,
-               out: Tensor, weight_t: Optional[Tensor] = None) -> None:
-    """Causal depthwise conv + SiLU over all tokens of the step; reads the windows.
+               out: Tensor, weight_t: Optional[Tensor] = None, activation: bool = True) -> None:
+    """Causal depthwise conv + SiLU (``activation`` False: the conv alone) over all tokens of the step; reads the windows.
     ``weight_t`` is the tap-major copy [K, C] of ``weight`` [C, K]; with it bfloat16 inputs take
     the vector kernel."""
     _cuda(x, pre_scale, pre_bias, weight, bias, window, seq_of, cu, slots, out, weight_t)
@@ -435,7 +449,7 @@ def conv1d_fwd(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], weight:
         raise KernelError("conv1d: weight_t must be contiguous float32 [K, C]")
     _call("pmm_conv1d_fwd", x.data_ptr(), ld, pre_scale.data_ptr(), _ptr(pre_bias), weight.data_ptr(),
           _ptr(weight_t), _ptr(bias), window.data_ptr(), seq_of.data_ptr(), cu.data_ptr(), slots.data_ptr(),
-          out.data_ptr(), T, C, K, _dt(x), _stream())
+          out.data_ptr(), T, C, K, _dt(x), int(bool(activation)), _stream())
 
 
 def conv1d_window_update(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], window: Tensor,
@@ -449,8 +463,10 @@ def conv1d_window_update(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor
 
 
 def conv1d_decode(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], weight: Tensor,
-                  bias: Optional[Tensor], window: Tensor, slots: Tensor, out: Tensor) -> None:
-    """Conv + SiLU + window shift for a step in which every sequence brings one token."""
+                  bias: Optional[Tensor], window: Tensor, slots: Tensor, out: Tensor,
+                  activation: bool = True) -> None:
+    """Conv + SiLU (``activation`` False: the conv alone) + window shift for a step in which every
+    sequence brings one token."""
     _cuda(x, pre_scale, pre_bias, weight, bias, window, slots, out)
     ld = _rows_view(x, "conv1d: x")
     n_seq = x.shape[0]
@@ -463,7 +479,7 @@ def conv1d_decode(x: Tensor, pre_scale: Tensor, pre_bias: Optional[Tensor], weig
         raise KernelError("conv1d: out must be [T, C]")
     _call("pmm_conv1d_decode", x.data_ptr(), ld, pre_scale.data_ptr(), _ptr(pre_bias),
           weight.data_ptr(), _ptr(bias), window.data_ptr(), slots.data_ptr(), out.data_ptr(), n_seq, C,
-          K, _dt(x), _stream())
+          K, _dt(x), int(bool(activation)), _stream())
 
 
 def _gate_args(gate, out: Tensor, what: str):
@@ -640,23 +656,28 @@ def ssm_scan_tc(xbc: Tensor, dt_raw: Tensor, dt_scale: float, dt_shift: Tensor, 
 
 def gated_norm(y: Tensor, z_raw: Tensor, z_scale: float, z_bias: Optional[Tensor],
                weight: Optional[Tensor], eps: float, n_groups: int, norm_before_gate: bool,
-               out: Tensor) -> None:
-    """out = y*silu(z), optionally RMS-normalised per group of channels (before or after the gate)."""
+               out: Tensor, gate: str = "silu") -> None:
+    """out = y*silu(z), optionally RMS-normalised per group of channels (before or after the gate).
+    ``gate`` "sigmoid": sigmoid(z) in place of silu(z).  y may be float32 whatever the type of z and
+    out (a recurrence's output)."""
     _cuda(y, z_raw, z_bias, weight, out)
     T, I = y.shape
-    if not (y.is_contiguous() and out.is_contiguous() and out.shape == y.shape and out.dtype == y.dtype):
-        raise KernelError("gated_norm: y and out must be contiguous [T, I] of one type")
+    if not (y.is_contiguous() and out.is_contiguous() and out.shape == y.shape
+            and y.dtype in (out.dtype, torch.float32)):
+        raise KernelError("gated_norm: y and out must be contiguous [T, I]; y of out's type or float32")
+    if gate not in ("silu", "sigmoid"):
+        raise KernelError("gated_norm: the gate is 'silu' or 'sigmoid'")
     ld_z = _rows_view(z_raw, "gated_norm: z")
-    if not (z_raw.shape == y.shape and z_raw.dtype == y.dtype):
-        raise KernelError("gated_norm: z must match y")
+    if not (z_raw.shape == y.shape and z_raw.dtype == out.dtype):
+        raise KernelError("gated_norm: z must match out")
     _f32vec(z_bias, I, "gated_norm: z_bias")
     _f32vec(weight, I, "gated_norm: weight")
     groups = n_groups if weight is not None else 1
     if not (I % groups == 0):
         raise KernelError("gated_norm: width must be a multiple of the group count")
     _call("pmm_gated_norm", y.data_ptr(), z_raw.data_ptr(), ld_z, float(z_scale), _ptr(z_bias),
-          _ptr(weight), float(eps), int(bool(norm_before_gate)), out.data_ptr(), T, I, groups, _dt(y),
-          _stream())
+          _ptr(weight), float(eps), int(bool(norm_before_gate)), out.data_ptr(), T, I, groups, _dt(out),
+          int(y.dtype == torch.float32 and out.dtype != torch.float32), int(gate == "sigmoid"), _stream())
 
 
 def check_head_dim(head_dim: int) -> None:
@@ -755,8 +776,11 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
                     window: int = 0, n_splits: int = 1, split_len: int = 0,
                     scratch: Optional[Tensor] = None, cu_seqlens: Optional[Tensor] = None,
                     new_lens: Optional[Sequence[int]] = None, use_tensor_cores: bool = True,
-                    split_counter: Optional[Tensor] = None, tile_rows: Optional[int] = None) -> None:
+                    split_counter: Optional[Tensor] = None, tile_rows: Optional[int] = None,
+                    sink: Optional[Tensor] = None) -> None:
     """Causal attention of every token over keys lo..pos of its request in the paged cache.
+    ``sink`` (one float per query head): the softmax's denominator also holds exp(sink[h]), a score
+    without key or value (float kernel only).
     With ``cu_seqlens`` and ``new_lens`` (tokens per sequence, host values) a bfloat16 cache of a
     supported shape goes to the tensor-core kernel; everything else to the float kernel.
     ``split_counter`` (int32, zero between calls, at least tiles x kv heads entries) lets the
@@ -786,8 +810,9 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
             raise KernelError("attention: split_len must be a positive multiple of 32")
         part_o = scratch.data_ptr()
         part_ml = part_o + 4 * T * n_q_heads * n_splits * head_dim
-    flash = (use_tensor_cores and q.dtype == torch.bfloat16 and cu_seqlens is not None and new_lens is not None
-             and flash_supported(n_q_heads, n_kv_heads, head_dim))
+    _f32vec(sink, n_q_heads, "attention: sink")
+    flash = (use_tensor_cores and sink is None and q.dtype == torch.bfloat16 and cu_seqlens is not None
+             and new_lens is not None and flash_supported(n_q_heads, n_kv_heads, head_dim))
     if flash:
         _i32(cu_seqlens, "attention: cu_seqlens")
         group = n_q_heads // n_kv_heads
@@ -813,7 +838,7 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
         _call("pmm_paged_attention", q.data_ptr(), pool.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], positions.data_ptr(), seq_of.data_ptr(), out.data_ptr(), part_o, part_ml,
               float(softmax_scale), int(window), int(split_len), int(n_splits), pool.shape[2], T, n_q_heads,
-              n_kv_heads, head_dim, _dt(q), _stream())
+              n_kv_heads, head_dim, _dt(q), _ptr(sink), _stream())
     if n_splits > 1:
         _call("pmm_flash_combine", part_o, part_ml, out.data_ptr(), T * n_q_heads, int(n_splits), head_dim,
               _dt(out), _stream())
@@ -1358,6 +1383,156 @@ def l2_prefetch(tensors: Sequence[Tensor]) -> None:
         sizes = (ctypes.c_longlong * len(part))(*[t.numel() * t.element_size() for t in part])
         _call("pmm_l2_prefetch", ctypes.cast(ptrs, ctypes.c_void_p), ctypes.cast(sizes, ctypes.c_void_p), len(part),
               _stream())
+
+
+# ----------------------------------------------------------------------------- residual lanes, normed sums
+HC_MAX_LANES = 8
+
+
+def hc_mix_norm(lanes_in: Tensor, lanes_out: Optional[Tensor], y: Optional[Tensor], mix: Optional[Tensor],
+                out_w: Optional[Tensor], in_w: Optional[Tensor], norm_w: Optional[Tensor], eps: float,
+                normed: Optional[Tensor], rows: Optional[Tensor] = None) -> None:
+    """Residual state in n lanes [n, T, D] (float32).  Folds a sublayer's result y into the lanes,
+    x_t <- sum_s mix[s, t] x_s + out_w[t] y (when y is given), writes them to ``lanes_out`` (may be
+    ``lanes_in``; not written with ``rows``), and writes normed = rmsnorm(sum_s in_w[s] x_s) * norm_w
+    (when asked for; of the listed rows only, with ``rows``).  ``lanes_in`` may be one [T, D] that every
+    lane starts from (expanded without a copy: lane stride 0)."""
+    _cuda(lanes_in, lanes_out, y, mix, out_w, in_w, norm_w, normed, rows)
+    if lanes_out is not None:
+        n, T, D = lanes_out.shape
+    else:
+        n, T, D = lanes_in.shape
+    if not (lanes_in.dtype == torch.float32 and lanes_in.shape == (n, T, D) and lanes_in.stride(2) == 1
+            and lanes_in.stride(1) == D and 1 <= n <= HC_MAX_LANES):
+        raise KernelError("hc_mix_norm: lanes must be float32 [n <= 8, T, D] with contiguous rows")
+    if lanes_out is not None and not (lanes_out.dtype == torch.float32 and lanes_out.is_contiguous()):
+        raise KernelError("hc_mix_norm: lanes_out must be contiguous float32 [n, T, D]")
+    y_dt = 0
+    if y is not None:
+        if not (y.shape == (T, D) and y.is_contiguous()):
+            raise KernelError("hc_mix_norm: y must be contiguous [T, D]")
+        _f32vec(mix, n * n, "hc_mix_norm: mix")
+        _f32vec(out_w, n, "hc_mix_norm: out_w")
+        y_dt = _dt(y)
+    R = T
+    if rows is not None:
+        _i32(rows, "hc_mix_norm: rows")
+        R = rows.numel()
+    dt = 0
+    if normed is not None:
+        _f32vec(in_w, n, "hc_mix_norm: in_w")
+        _f32vec(norm_w, D, "hc_mix_norm: norm_w")
+        if not (normed.shape == (R, D) and normed.is_contiguous()):
+            raise KernelError("hc_mix_norm: normed must be contiguous [rows, D]")
+        if D * 4 > 200 * 1024:
+            raise KernelError(f"hc_mix_norm: width {D} exceeds one block's shared memory")
+        dt = _dt(normed)
+    _call("pmm_hc_mix_norm", lanes_in.data_ptr(), lanes_in.stride(0), _ptr(lanes_out),
+          lanes_out.stride(0) if lanes_out is not None else 0, n, _ptr(y), _ptr(mix), _ptr(out_w), _ptr(in_w),
+          _ptr(norm_w), float(eps), _ptr(normed), _ptr(rows), R, D, dt, y_dt, _stream())
+
+
+def normed_sum(branches: Sequence[Tuple[Tensor, Tensor]], eps: float, scale: float, out: Tensor) -> None:
+    """out = scale * sum_b rmsnorm(x_b) * w_b over up to four (x_b [T, D], w_b [D] float32); out is
+    float32 or of the branches' type."""
+    xs = [b[0] for b in branches]
+    _cuda(out, *xs, *[b[1] for b in branches])
+    T, D = out.shape
+    if not (1 <= len(branches) <= 4 and out.is_contiguous()):
+        raise KernelError("normed_sum: one to four branches, contiguous out")
+    for x, w in branches:
+        if not (x.shape == (T, D) and x.dtype == xs[0].dtype):
+            raise KernelError("normed_sum: branches must be [T, D] of one type")
+        _rows_view(x, "normed_sum: branch")
+        _f32vec(w, D, "normed_sum: weight")
+    if not (out.dtype in (torch.float32, xs[0].dtype)):
+        raise KernelError("normed_sum: out must be float32 or of the branches' type")
+    n = len(branches)
+    ptrs = (ctypes.c_void_p * n)(*[x.data_ptr() for x in xs])
+    lds = (ctypes.c_longlong * n)(*[x.stride(0) for x in xs])
+    ws = (ctypes.c_void_p * n)(*[w.data_ptr() for _, w in branches])
+    _call("pmm_normed_sum", ctypes.cast(ptrs, ctypes.c_void_p), ctypes.cast(lds, ctypes.c_void_p),
+          ctypes.cast(ws, ctypes.c_void_p), n, float(eps), float(scale), out.data_ptr(),
+          int(out.dtype == torch.float32 and xs[0].dtype != torch.float32), T, D, _dt(xs[0]), _stream())
+
+
+# ----------------------------------------------------------------------------- pair rotation + page write
+def rope_pairs_store(q: Tensor, k: Tensor, v: Tensor, inv_freq: Optional[Tensor], rot_dims: int, positions: Tensor,
+                     seq_of: Tensor, block_table: Tensor, pool: Tensor, q_out: Tensor, n_heads: int,
+                     n_kv_heads: int, dim: int, vdim: int, padded_dim: int) -> None:
+    """Rotates neighbouring pairs of the first ``rot_dims`` entries of every query and key head,
+    writes queries to q_out [T, H*Dp] and keys and values into their pages [pages, 2, page, G*Dp],
+    every head padded with zeros to Dp = ``padded_dim`` entries."""
+    _cuda(q, k, v, inv_freq, positions, seq_of, block_table, pool, q_out)
+    T = q.shape[0]
+    ld_q, ld_k, ld_v = (_rows_view(t, "rope_pairs_store") for t in (q, k, v))
+    if not (q.shape[1] == n_heads * dim and k.shape == (T, n_kv_heads * dim) and v.shape == (T, n_kv_heads * vdim)
+            and q.dtype == k.dtype == v.dtype == pool.dtype == q_out.dtype):
+        raise KernelError("rope_pairs_store: q [T, H*d], k [T, G*d], v [T, G*dv] of the pool's type")
+    if not (pool.dim() == 4 and pool.shape[1] == 2 and pool.shape[3] == n_kv_heads * padded_dim and pool.is_contiguous()
+            and q_out.shape == (T, n_heads * padded_dim) and q_out.is_contiguous()):
+        raise KernelError("rope_pairs_store: pool [pages, 2, page_size, G*Dp], q_out [T, H*Dp]")
+    if rot_dims > 0:
+        _f32vec(inv_freq, rot_dims // 2, "rope_pairs_store: inv_freq")
+    _i32(positions, "rope_pairs_store: positions")
+    _i32(seq_of, "rope_pairs_store: seq_of")
+    _i32(block_table, "rope_pairs_store: block_table")
+    _call("pmm_rope_pairs_store", q.data_ptr(), ld_q, k.data_ptr(), ld_k, v.data_ptr(), ld_v, _ptr(inv_freq),
+          positions.data_ptr(), seq_of.data_ptr(), block_table.data_ptr(), block_table.shape[1], pool.data_ptr(),
+          pool.shape[2], q_out.data_ptr(), T, n_heads, n_kv_heads, dim, vdim, padded_dim, int(rot_dims), _dt(q),
+          _stream())
+
+
+# ----------------------------------------------------------------------------- matrix-state recurrences
+RECURRENT_MAX_KEY_DIM = 256
+
+
+def _recurrent_common(q: Tensor, k: Tensor, v: Tensor, state: Tensor, cu: Tensor, slots: Tensor, out: Tensor,
+                      H: int, Hk: int, d: int, dv: int, what: str) -> Tuple[int, int, int, int]:
+    T = q.shape[0]
+    lds = tuple(_rows_view(t, what) for t in (q, k, v))
+    if not (q.shape == (T, Hk * d) and k.shape == (T, Hk * d) and v.shape == (T, H * dv) and q.dtype == k.dtype == v.dtype):
+        raise KernelError(f"{what}: q, k [T, Hk*d], v [T, H*dv] of one type")
+    if not (state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, d, dv)):
+        raise KernelError(f"{what}: state must be contiguous float32 [slots, H, d, dv]")
+    if not (out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, H * dv)):
+        raise KernelError(f"{what}: out must be contiguous float32 [T, H*dv]")
+    if not (1 <= d <= RECURRENT_MAX_KEY_DIM):
+        raise KernelError(f"{what}: key sizes up to {RECURRENT_MAX_KEY_DIM}")
+    _i32(cu, f"{what}: cu_seqlens")
+    _i32(slots, f"{what}: slots")
+    return (T,) + lds
+
+
+def delta_scan(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, a: Tensor, dt_bias: Tensor, a_log: Tensor,
+               state: Tensor, cu: Tensor, slots: Tensor, n_seq: int, out: Tensor, n_heads: int, n_qk_heads: int,
+               dim: int, vdim: int, unit_eps: float, q_scale: float) -> None:
+    """Gated delta rule, token by token, state [slots, H, d, dv] float32 carried between steps:
+    S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q with g = exp(-exp(a_log_h)
+    softplus(a + dt_bias)) per head and key channel, beta = sigmoid(beta_raw), q and k scaled to unit
+    length (x / sqrt(sum x^2 + unit_eps); q also by q_scale)."""
+    _cuda(q, k, v, beta, a, dt_bias, a_log, state, cu, slots, out)
+    T, ld_q, ld_k, ld_v = _recurrent_common(q, k, v, state, cu, slots, out, n_heads, n_qk_heads, dim, vdim, "delta_scan")
+    ld_b, ld_a = _rows_view(beta, "delta_scan: beta"), _rows_view(a, "delta_scan: a")
+    if not (beta.shape == (T, n_heads) and a.shape == (T, n_heads * dim) and beta.dtype == a.dtype == q.dtype):
+        raise KernelError("delta_scan: beta [T, H], a [T, H*d] of q's type")
+    _f32vec(dt_bias, n_heads * dim, "delta_scan: dt_bias")
+    _f32vec(a_log, n_heads, "delta_scan: a_log")
+    _call("pmm_delta_scan", q.data_ptr(), ld_q, k.data_ptr(), ld_k, v.data_ptr(), ld_v, beta.data_ptr(), ld_b,
+          a.data_ptr(), ld_a, dt_bias.data_ptr(), a_log.data_ptr(), state.data_ptr(), cu.data_ptr(), slots.data_ptr(),
+          out.data_ptr(), int(n_seq), n_heads, n_qk_heads, dim, vdim, float(unit_eps), float(q_scale), _dt(q), _stream())
+
+
+def decay_scan(q: Tensor, k: Tensor, v: Tensor, decay: Tensor, state: Tensor, cu: Tensor, slots: Tensor, n_seq: int,
+               out: Tensor, n_heads: int, dim: int, vdim: int) -> None:
+    """Linear attention with one decay per head, token by token: S <- decay_h S + k v^T; o = S^T q with
+    q, k, v = silu of the given projections; state [slots, H, d, dv] float32 carried between steps."""
+    _cuda(q, k, v, decay, state, cu, slots, out)
+    T, ld_q, ld_k, ld_v = _recurrent_common(q, k, v, state, cu, slots, out, n_heads, n_heads, dim, vdim, "decay_scan")
+    _f32vec(decay, n_heads, "decay_scan: decay")
+    _call("pmm_decay_scan", q.data_ptr(), ld_q, k.data_ptr(), ld_k, v.data_ptr(), ld_v, decay.data_ptr(),
+          state.data_ptr(), cu.data_ptr(), slots.data_ptr(), out.data_ptr(), int(n_seq), n_heads, dim, vdim, _dt(q),
+          _stream())
 
 
 def ensure_built() -> str:

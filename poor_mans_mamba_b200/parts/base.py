@@ -26,7 +26,7 @@ class ParamSpec:
     kind: "matrix"  -> kept in the compute type (bfloat16 or float32);
           "vector"  -> always float32 on the device (norm weights, biases, per-head scalars);
           "table"   -> integer table, int32.
-    init: how the random-weights mode fills it: ("normal", std) | ("ones",) | ("zeros",) |
+    init: how the random-weights mode fills it: ("normal", std) | ("ones",) | ("zeros",) | ("uniform", lo, hi) |
           ("log_uniform", lo, hi) [log of U(lo,hi)] | ("inv_softplus_log_uniform", lo, hi).
     alt_shapes: other stored shapes with the same element count that are accepted and
           viewed as ``shape`` (e.g. a conv weight stored [C, 1, K]).
@@ -249,6 +249,10 @@ class ModelSpec:
     head_multiplier: float
     eos_token_id: int = -1
     bos_token_id: int = 0
+    # None: one residual stream [T, D].  n >= 1: the residual state is n lanes [n, T, D], all equal to
+    # the embedding's output at the start and summed before the final norm (arrangements that mix
+    # lanes, such as ``hyper_prenorm``, read and write them through the ResidualStream)
+    residual_lanes: Optional[int] = None
 
 
 # ----------------------------------------------------------------------------- registries

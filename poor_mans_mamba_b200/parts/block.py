@@ -38,15 +38,34 @@ def prenorm_layer(prefix: str, mixer_norm: PartSpec, mixers, ffn_norm: Optional[
                                                   "ffn_norm": ffn_norm, "ffn": ffn})
 
 
+_LANE_ONES = {}
+
+
+def _lane_ones(n: int, device) -> Tensor:
+    key = (n, torch.device(device))
+    if key not in _LANE_ONES:
+        _LANE_ONES[key] = torch.ones(n, dtype=torch.float32, device=device)
+    return _LANE_ONES[key]
+
+
 class ResidualStream:
     """The float32 hidden state [T, D] of a step plus the branches waiting to be added."""
 
-    def __init__(self, h: Tensor, ctx, n_branch_buffers: int):
+    def __init__(self, h: Tensor, ctx, n_branch_buffers: int, lanes: Optional[int] = None):
         self.h = h
         self.ctx = ctx
         self.pending: List[Tuple[Tensor, float]] = []
         self._buffers = [ctx.workspace.alloc(tuple(h.shape), ctx.dtype) for _ in range(n_branch_buffers)]
         self._taken = 0
+        # Residual state in lanes [n, T, D] (see ModelSpec.residual_lanes): every lane starts as h, so
+        # until the first write the lanes are read from h itself (a view with lane stride 0).
+        self.lanes: Optional[Tensor] = None
+        self._lanes_fresh = False
+        self.lane_pending: Optional[Tuple[Tensor, Tensor, Tensor]] = None
+        if lanes is not None:
+            self.lanes = ctx.workspace.alloc((int(lanes),) + tuple(h.shape), torch.float32)
+            self._lanes_fresh = True
+            self._ones = _lane_ones(int(lanes), h.device)
 
     def take_branch(self) -> Tensor:
         """A [T, D] buffer in the storage type for a part to write its output into."""
@@ -59,9 +78,36 @@ class ResidualStream:
     def add(self, branch: Tensor, scale: float) -> None:
         self.pending.append((branch, float(scale)))
 
+    def lane_add(self, y: Tensor, mix: Tensor, out_w: Tensor) -> None:
+        """A sublayer's result waits to enter the lanes: x_t <- sum_s mix[s, t] x_s + out_w[t] y."""
+        if self.lane_pending is not None:
+            raise RuntimeError("a sublayer's result is already waiting to enter the lanes")
+        self.lane_pending = (y, mix, out_w)
+
+    def lanes_normed(self, in_w: Tensor, norm: Norm, rows: Optional[Tensor] = None) -> Tensor:
+        """Fold the waiting result into the lanes and return norm(sum_s in_w[s] x_s) (of the selected
+        rows only, if given: then the lanes are left as they are).  One launch."""
+        pro = norm.rms_prologue()
+        if self.lanes is None or pro is None:
+            raise RuntimeError("lanes_normed needs a residual state in lanes and an RMS norm")
+        weight, eps = pro
+        n_rows = self.h.shape[0] if rows is None else rows.numel()
+        out = self.ctx.workspace.alloc((n_rows, self.h.shape[1]), self.ctx.dtype)
+        src = self.h.unsqueeze(0).expand(self.lanes.shape) if self._lanes_fresh else self.lanes
+        y, mix, out_w = self.lane_pending if self.lane_pending is not None else (None, None, None)
+        K.hc_mix_norm(src, self.lanes if rows is None else None, y, mix, out_w, in_w, weight, eps, out, rows)
+        if rows is None:
+            self._lanes_fresh = self._lanes_fresh and y is None
+            self.lane_pending = None
+            self._taken = 0
+        return out
+
     def normed(self, norm: Norm, rows: Optional[Tensor] = None) -> Tensor:
         """Fold the pending branches into the stream and return norm(stream) (of the selected
-        rows only, if given: then the stream itself is left unchanged)."""
+        rows only, if given: then the stream itself is left unchanged).  With a residual state in
+        lanes the stream is their sum."""
+        if self.lanes is not None:
+            return self.lanes_normed(self._ones, norm, rows)
         n_rows = self.h.shape[0] if rows is None else rows.numel()
         out = self.ctx.workspace.alloc((n_rows, self.h.shape[1]), self.ctx.dtype)
         norm.forward(self.h, self.pending, out, rows, self.ctx)
@@ -71,6 +117,8 @@ class ResidualStream:
         return out
 
     def flush(self) -> Tensor:
+        if self.lanes is not None:
+            raise RuntimeError("a residual state in lanes has no single stream to flush into")
         fold_branches(self.h, self.pending)
         self.pending = []
         self._taken = 0

@@ -31,7 +31,8 @@ _TC_ENABLED = os.environ.get("PMM_TCGEN05_FFN", "1") == "1"
 
 class SwiGLU(FeedForward):
     def __init__(self, hidden_size: int, intermediate_size: int, gate_multiplier: float = 1.0,
-                 down_multiplier: float = 1.0):
+                 down_multiplier: float = 1.0, tensors=("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
+        self.tensors = tuple(tensors)  # names of the gate, up and down matrices within the part
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
         self.gate_multiplier = float(gate_multiplier)
@@ -41,12 +42,13 @@ class SwiGLU(FeedForward):
 
     def param_specs(self) -> List[ParamSpec]:
         f, d = self.intermediate_size, self.hidden_size
-        return [ParamSpec("gate_proj.weight", (f, d)), ParamSpec("up_proj.weight", (f, d)),
-                ParamSpec("down_proj.weight", (d, f))]
+        g, u, dn = self.tensors
+        return [ParamSpec(g, (f, d)), ParamSpec(u, (f, d)), ParamSpec(dn, (d, f))]
 
     def bind(self, params: Dict[str, Tensor]) -> None:
-        self.gate_up = torch.cat([params["gate_proj.weight"], params["up_proj.weight"]], dim=0).contiguous()
-        self.down = params["down_proj.weight"].contiguous()
+        g, u, dn = self.tensors
+        self.gate_up = torch.cat([params[g], params[u]], dim=0).contiguous()
+        self.down = params[dn].contiguous()
 
     def forward(self, x: Tensor, ctx, out: Tensor) -> None:
         T = x.shape[0]

@@ -1,7 +1,8 @@
 """RMSNorm with the residual additions folded in.
 
 y = x * (1/sqrt(mean(x^2) + eps)) * w; eps inside the root, the weight multiplies after
-normalisation (reference src/ops/cpu/rms_norm.cpp:11-16).  Statistics are float32.
+normalisation (reference src/ops/cpu/rms_norm.cpp:11-16).  Statistics are float32.  A weight
+stored around zero (y = ... * (1 + w)) is the same norm with ``offset`` 1.
 """
 from __future__ import annotations
 
@@ -24,16 +25,24 @@ def fold_branches(h: Tensor, pending) -> None:
 
 
 class RMSNorm(Norm):
-    def __init__(self, width: int, eps: float):
+    """``offset``: the stored weight is kept around zero and the norm multiplies by offset + w (the sum
+    is made once, in float32, when the tensors are bound).  ``tensor``: the weight's name within the
+    part ("" where the part's own name is the tensor's)."""
+
+    def __init__(self, width: int, eps: float, offset: float = 0.0, tensor: str = "weight"):
         self.width = int(width)
         self.eps = float(eps)
+        self.offset = float(offset)
+        self.tensor = str(tensor)
         self.weight: Optional[Tensor] = None
 
     def param_specs(self) -> List[ParamSpec]:
-        return [ParamSpec("weight", (self.width,), kind="vector", init=("ones",))]
+        init = ("ones",) if self.offset == 0.0 else ("normal", 0.1)
+        return [ParamSpec(self.tensor, (self.width,), kind="vector", init=init)]
 
     def bind(self, params: Dict[str, Tensor]) -> None:
-        self.weight = params["weight"]
+        w = params[self.tensor]
+        self.weight = w if self.offset == 0.0 else (w + self.offset).contiguous()
 
     def rms_prologue(self):
         return self.weight, self.eps

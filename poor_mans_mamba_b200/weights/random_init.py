@@ -42,6 +42,9 @@ def make_tensor(spec: ParamSpec, seed: int, full_name: str) -> torch.Tensor:
         t = torch.ones(shape, dtype=torch.float32)
     elif kind == "zeros":
         t = torch.zeros(shape, dtype=torch.float32)
+    elif kind == "uniform":
+        lo, hi = float(spec.init[1]), float(spec.init[2])
+        t = lo + (hi - lo) * torch.rand(shape, generator=g, dtype=torch.float32)
     elif kind == "log_uniform":  # log of a uniform draw from [lo, hi]
         lo, hi = float(spec.init[1]), float(spec.init[2])
         t = torch.log(lo + (hi - lo) * torch.rand(shape, generator=g, dtype=torch.float32))
@@ -63,7 +66,7 @@ def write_random_model(config: Dict[str, Any], seed: int, out_dir: str, store_dt
     if store_dtype not in ("bfloat16", "float32"):
         raise ValueError("store_dtype must be 'bfloat16' or 'float32'")
     arch = resolve_architecture(config)
-    cfg = arch.parse_config(config)
+    cfg = arch.parse(config)
     model = Model(arch.model_spec(cfg))
     tensors = {}
     for name, spec in model.param_specs().items():
