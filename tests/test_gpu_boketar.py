@@ -1,0 +1,179 @@
+"""Boketar through the engine against the plain implementation (GPU): every way of cutting the
+work, three tiny configurations that differ in every size and option, float32 and bfloat16."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import boketar_configs as B
+import gpu_harness as H
+from plain import boketar_plain as P
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+F32_FRAC = 2e-5
+LENGTHS = (1, 2, 9, 40, 77, 131, 203)
+
+
+def refs_of(cfg, weights, seqs):
+    return [P.forward(cfg, weights, s, torch.float64) for s in seqs]
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C"])
+def case(request, tmp_path_factory):
+    which = request.param
+    d, cfg, weights = B.make_model_dir(which, str(tmp_path_factory.mktemp(f"bk{which}")), seed=ord(which))
+    seqs = B.sequences(cfg, LENGTHS, seed=7)
+    return which, d, cfg, weights, seqs, refs_of(cfg, weights, seqs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
+def test_cuttings_agree_with_plain(case, dtype, cutting):
+    which, d, cfg, weights, seqs, refs = case
+    page_size = 16
+    if cutting == "mixed":
+        # so few pages and slots that they are used again
+        budget = max((len(s) + page_size - 1) // page_size for s in seqs) + 5
+        runner = H.make_runner(d, dtype, page_size=page_size, num_pages=budget, num_slots=3)
+        script = H.script_mixed(seqs, max_live=3, seed=5, budget_pages=budget, page_size=page_size)
+        assert any(len(p) > 1 and any(n == 1 for _, _, n in p) and any(n > 1 for _, _, n in p) for p, _ in script)
+    else:
+        runner = H.make_runner(d, dtype, page_size=page_size, num_pages=16, num_slots=2)
+        script = {"whole": H.script_whole, "portions": H.script_portions,
+                  "tail": lambda s: H.script_tail_one_by_one(s, tail=70)}[cutting](seqs)
+    out = H.run_script(runner, seqs, script)
+    for i, ref in enumerate(refs):
+        H.check_rows(out[i], ref, dtype, f"{which} {dtype} {cutting} seq {i} (len {len(seqs[i])})", f32_frac=F32_FRAC)
+    for g in runner.cache.groups.values():
+        assert g.pool.n_free == g.num_pages  # every page came back
+    assert runner.cache.free_slots == runner.cache.num_slots
+
+
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_portions_of_two_tokens_and_page_borders(case, page_size):
+    """Every portion is two tokens long (then three, so that both parities of a page's and a window's
+    edge are met), against the whole prompt."""
+    which, d, cfg, weights, seqs, refs = case
+    i = 5
+    for width in (2, 3):
+        runner = H.make_runner(d, "float32", page_size=page_size, num_pages=max(4, 256 // page_size), num_slots=1)
+        n = len(seqs[i])
+        script = [([(i, a, min(width, n - a))], [i] if a + width >= n else []) for a in range(0, n, width)]
+        out = H.run_script(runner, seqs, script)
+        H.check_rows(out[i], refs[i], "float32", f"{which} portions of {width}", f32_frac=F32_FRAC)
+
+
+def test_long_decoding_from_the_first_token(case):
+    """One prompt token, then 202 tokens one by one: windows pass over decoded tokens only, the
+    recurrences' states are carried 200 steps."""
+    which, d, cfg, weights, seqs, refs = case
+    for dtype in ("float32", "bfloat16"):
+        runner = H.make_runner(d, dtype, page_size=16, num_pages=16, num_slots=1)
+        out = H.run_script(runner, seqs[6:7], H.script_tail_one_by_one(seqs[6:7], tail=len(seqs[6]) - 1))
+        H.check_rows(out[0], refs[6], dtype, f"{which} {dtype} long decoding", f32_frac=F32_FRAC)
+
+
+def test_batch_of_unequal_requests_equals_each_alone(case):
+    which, d, cfg, weights, seqs, refs = case
+    for dtype in ("float32", "bfloat16"):
+        runner = H.make_runner(d, dtype, page_size=16, num_pages=40, num_slots=4)
+        pick = [1, 3, 4, 6]
+        # first halves together, then the second halves beside single tokens of a request that decodes
+        half = {i: len(seqs[i]) // 2 for i in pick}
+        script = [([(i, 0, half[i]) for i in pick], []),
+                  ([(i, half[i], len(seqs[i]) - half[i]) for i in pick], pick)]
+        out = H.run_script(runner, seqs, script)
+        for i in pick:
+            H.check_rows(out[i], refs[i], dtype, f"{which} {dtype} batched seq {i}", f32_frac=F32_FRAC)
+
+
+def test_loud_far_state_and_sink(tmp_path):
+    """Weights under which a lost state, a lost sink or a window that is one token off cannot hide:
+    the decays of the linear attention are one (nothing fades: the first token weighs as much as the
+    last), the delta rule barely forgets, the sinks are large, and the window attention's queries
+    and keys are scaled so that single scores stand out."""
+    def loud(cfg):
+        for layer in cfg["layers"]:
+            if layer["type"] == "parallel":
+                layer["mixer"]["right"]["decay"] = [1.0] * layer["mixer"]["right"]["heads"]
+                layer["mixer"]["left"]["scale"] *= 6.0
+    d, cfg, weights = B.make_model_dir("A", str(tmp_path), seed=11, patch=loud)
+    for k in list(weights):
+        if k.endswith("left.sink"):
+            weights[k] = weights[k] + 4.0
+        if k.endswith("mix.dt_bias"):
+            weights[k] = weights[k] - 4.0
+    from poor_mans_mamba_b200.weights import save_file
+    save_file({k: v.to(torch.bfloat16) for k, v in weights.items()}, os.path.join(d, "model.safetensors"))
+    weights = {k: v.to(torch.bfloat16).float() for k, v in weights.items()}
+    seqs = B.sequences(cfg, (300,), seed=3)
+    ref = P.forward(cfg, weights, seqs[0], torch.float64)
+    # the oracle itself: without the sink, or with the window one token longer, the logits move visibly
+    no_sink = {k: (v - 60.0 if k.endswith("left.sink") else v) for k, v in weights.items()}
+    assert float((P.forward(cfg, no_sink, seqs[0][:60]) - ref[:60]).abs().max()) > 0.05
+    wider = json.loads(json.dumps(cfg))
+    wider["layers"][0]["mixer"]["left"]["mask"]["size"] += 1
+    assert float((P.forward(wider, weights, seqs[0][:60]) - ref[:60]).abs().max()) > 0.05
+    for dtype in ("float32", "bfloat16"):
+        for script in (H.script_whole(seqs), H.script_tail_one_by_one(seqs, tail=64), H.script_portions(seqs, seed=2)):
+            runner = H.make_runner(d, dtype, page_size=16, num_pages=24, num_slots=1)
+            out = H.run_script(runner, seqs, script)
+            H.check_rows(out[0], ref, dtype, f"loud {dtype}", f32_frac=4e-5)
+
+
+def test_greedy_generation_through_the_engine(case):
+    """Engine.generate (scheduler, sampler, decode graphs) against greedy decoding with the plain
+    implementation, float32; bfloat16 with graphs against bfloat16 step by step."""
+    from poor_mans_mamba_b200.entry import Engine
+    which, d, cfg, weights, seqs, refs = case
+    prompts = [seqs[2], seqs[3][:23], seqs[1]]
+    n_new = 12
+    eng = Engine(d, dtype="float32", max_tokens=1024, max_seqs=4, page_size=16, max_batched_tokens=32)
+    got = eng.generate(prompts, max_new_tokens=n_new, eos_token_id=-1)
+    for p, g in zip(prompts, got):
+        toks = list(p)
+        for _ in range(n_new):
+            lg = P.forward(cfg, weights, toks, torch.float64)[-1]
+            top2 = torch.topk(lg, 2).values
+            if float(top2[0] - top2[1]) < 1e-3:
+                break  # a near tie: the two may disagree from here on without either being wrong
+            toks.append(int(lg.argmax()))
+        want = toks[len(p):]
+        assert g[:len(want)] == want
+    a = Engine(d, dtype="bfloat16", max_tokens=1024, max_seqs=4, page_size=16, cuda_graphs=True).generate(
+        prompts, max_new_tokens=n_new, eos_token_id=-1)
+    b = Engine(d, dtype="bfloat16", max_tokens=1024, max_seqs=4, page_size=16, cuda_graphs=False).generate(
+        prompts, max_new_tokens=n_new, eos_token_id=-1)
+    assert a == b
+
+
+def test_trace_program_replays_a_schedule(case, tmp_path):
+    which, d, cfg, weights, seqs, refs = case
+    if which != "A":
+        pytest.skip("one configuration is enough for the program")
+    steps = [
+        {"step": 0, "entries": [{"id": "x", "tokens": seqs[3][:17], "want": [0, 16]},
+                                {"id": "y", "tokens": seqs[2], "want": [8]}], "end": ["y"]},
+        {"step": 1, "entries": [{"id": "x", "tokens": seqs[3][17:19], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "x", "tokens": seqs[3][19:], "want": [len(seqs[3]) - 20]},
+                                {"id": "z", "tokens": seqs[1], "want": [1]}], "end": ["x", "z"]},
+    ]
+    out_dir = str(tmp_path / "out")
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", "float32",
+                           "--out", out_dir, "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    V = cfg["vocab"]
+    s0 = np.fromfile(os.path.join(out_dir, "0.f32"), dtype="<f4").reshape(-1, V)
+    s2 = np.fromfile(os.path.join(out_dir, "2.f32"), dtype="<f4").reshape(-1, V)
+    assert not os.path.exists(os.path.join(out_dir, "1.f32"))
+    want0 = torch.stack([refs[3][0], refs[3][16], refs[2][8]])
+    want2 = torch.stack([refs[3][-1], refs[1][1]])
+    H.check_rows(torch.from_numpy(s0), want0, "float32", "trace step 0", f32_frac=F32_FRAC)
+    H.check_rows(torch.from_numpy(s2), want2, "float32", "trace step 2", f32_frac=F32_FRAC)
