@@ -456,6 +456,145 @@ def mixed_workload(args, cfg, full_layers, nums, peaks, model_dir, checked) -> i
     return 0
 
 
+# ----------------------------------------------------------------------------- Boketar beside Falcon-H1
+# `--workload compare`: prefill and decode of a Boketar model beside a Falcon-H1 model of equal width,
+# feed-forward size, layer count and vocabulary (random weights), and the device time of every kernel
+# of one prompt step and one decode step of each.  name -> (width, ff, Boketar mixer sizes, changed
+# Falcon-H1 keys).
+COMPARE_SIZES = {
+    "0.5b": (1024, 2048,
+             dict(delta=dict(heads=8, kv_heads=8, dim=128, vdim=128, conv=4, decay_rank=64, gate_rank=64),
+                  left=dict(heads=8, kv_heads=2, dim=64, vdim=64, conv=3, window=1024),
+                  right=dict(heads=8, dim=64, vdim=128)), {}),
+    "7b": (3072, 12288,
+           dict(delta=dict(heads=24, kv_heads=12, dim=128, vdim=128, conv=4, decay_rank=128, gate_rank=128),
+                left=dict(heads=12, kv_heads=2, dim=128, vdim=128, conv=3, window=2048),
+                right=dict(heads=24, dim=128, vdim=128)), OTHER_SIZES["7b"][0]),
+}
+
+
+def boketar_config(width, ff, vocab, sizes, layers):
+    """`layers` layers, channel_delta and parallel in turn, every one with a feed-forward, two lanes."""
+    d, l, r = sizes["delta"], dict(sizes["left"]), sizes["right"]
+    window = l.pop("window")
+    left = dict(l, mask={"size": window}, rot={"dims": l["dim"], "base": 1e6}, scale=l["dim"] ** -0.5)
+    right = dict(r, decay=[1.0 - 2.0 ** -(4 + 6 * h / max(1, r["heads"] - 1)) for h in range(r["heads"])])
+    out = []
+    for i in range(layers):
+        mixer = dict(d) if i % 2 == 0 else {"left": left, "right": right}
+        out.append({"type": "channel_delta" if i % 2 == 0 else "parallel", "mixer": mixer,
+                    "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Boketar", "vocab": vocab, "width": width, "streams": 2, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "layers": out}
+
+
+def compare_workload(args, peaks) -> int:
+    import torch
+
+    from poor_mans_mamba_b200.engine.runner import StepEntry
+    from poor_mans_mamba_b200.entry import Engine
+    from poor_mans_mamba_b200.kernels import ops as K
+    from poor_mans_mamba_b200.weights import write_random_model
+
+    width, ff, bk_sizes, falcon_keys = COMPARE_SIZES[args.sizes]
+    layers = args.layers if args.layers is not None else 4
+    falcon = dict(CONFIG_05B)
+    falcon.update(falcon_keys)
+    falcon["num_hidden_layers"] = layers
+    vocab = falcon["vocab_size"]
+    configs = {"boketar": boketar_config(width, ff, vocab, bk_sizes, layers), "falcon_h1": falcon}
+    prompt, batch, ctx_len = args.prompt_tokens, args.batch, args.context
+    rng = random.Random(3)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")  # larger than the L2
+
+    def timed(fn, reps):
+        out = []
+        for _ in range(reps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            out.append(a.elapsed_time(b))
+        return statistics.median(out)
+
+    def kernel_times(fn):
+        """name -> device microseconds of every kernel of this repository and every library product that
+        `fn` issues (launch by launch, an event pair around each)."""
+        marks = []
+        call, mm = K._call, K._mm
+
+        def wrap(inner, label):
+            def go(*a, **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                r = inner(*a, **k)
+                e1.record()
+                marks.append((label(a), e0, e1))
+                return r
+            return go
+        K._call, K._mm = wrap(call, lambda a: a[0]), wrap(mm, lambda a: "library product")
+        try:
+            fn()
+            torch.cuda.synchronize()
+        finally:
+            K._call, K._mm = call, mm
+        out = {}
+        for name, e0, e1 in marks:
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1) * 1e3
+        return {k: round(v, 1) for k, v in sorted(out.items(), key=lambda kv: -kv[1])}
+
+    result = {}
+    with torch.cuda.device(0), ClockSampler() as clocks:
+        for name, cfg in configs.items():
+            tmp = tempfile.mkdtemp(prefix="pmm_bench_")
+            atexit.register(shutil.rmtree, tmp, ignore_errors=True)
+            write_random_model(cfg, seed=2, out_dir=tmp)
+            eng = Engine(tmp, dtype=args.dtype, max_tokens=(batch + 1) * (ctx_len + 64) + prompt + 64,
+                         max_seqs=batch + 1, page_size=64, max_batched_tokens=8192, max_seq_len=max(ctx_len, prompt) + 64)
+            run = eng.runner
+            toks = [rng.randrange(vocab) for _ in range(prompt)]
+            n = [0]
+
+            def prefill():
+                n[0] += 1
+                run.step([StepEntry(("p", n[0]), toks, [prompt - 1])])
+                run.finish(("p", n[0]))
+            for _ in range(max(3, args.warmup)):   # the shape is recorded into a graph when it comes again
+                prefill()
+            torch.cuda.synchronize()
+            pre_ms = timed(prefill, 5)
+            reqs = [("d", i) for i in range(batch)]
+            for r in reqs:
+                run.step([StepEntry(r, [rng.randrange(vocab) for _ in range(ctx_len - args.steps - 8)], [])])
+            run.decode_tokens(reqs, [rng.randrange(vocab) for _ in range(batch)])
+            for _ in range(max(3, args.warmup)):
+                run.decode_tokens(reqs, None)
+            torch.cuda.synchronize()
+            dec_ms = timed(lambda: run.decode_tokens(reqs, None), max(5, args.steps))
+            # every kernel of one prompt step and one decode step, issued launch by launch
+            run.graphs, graphs = None, run.graphs
+            prefill()
+            pre_k = kernel_times(prefill)
+            step = [StepEntry(r, [1], [0]) for r in reqs]
+            run.step(step)
+            dec_k = kernel_times(lambda: run.step(step))
+            run.graphs = graphs
+            for r in reqs:
+                run.finish(r)
+            result[name] = {"prefill_ms": round(pre_ms, 3), "prefill_tokens_per_s": round(prompt / pre_ms * 1e3, 1),
+                            "decode_ms_per_step": round(dec_ms, 4), "decode_tokens_per_s": round(batch / dec_ms * 1e3, 1),
+                            "prefill_kernels_us": pre_k, "decode_kernels_us": dec_k}
+            del eng, run
+            torch.cuda.empty_cache()
+    print(json.dumps({"workload": "compare", "sizes": args.sizes, "layers": layers, "width": width, "ff": ff,
+                      "vocab": vocab, "dtype": args.dtype, "data": "synthetic", "prompt_tokens": prompt,
+                      "decode_batch": batch, "decode_context": ctx_len, "l2": "flushed before every timed step",
+                      "boketar_sizes": bk_sizes, "clocks": clocks.summary(), "peaks": peaks, **result}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -471,12 +610,17 @@ def main() -> int:
                     "(same layer sizes) where memory or time needs it")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "serve"],
+    ap.add_argument("--prompt-tokens", type=int, default=2048, help="--workload compare: tokens of the prompt step")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "serve", "compare"],
                     help="decode: the benchmark (decode steps of a batch, with prefill and other points beside it); "
                          "mixed: one step of 32 decoding requests at contexts of 1,024..4,096 tokens beside four "
                          "prompt portions of 512 tokens, by default at Falcon-H1-1.5B-Deep layer sizes; "
                          "serve: bursts of 32 requests with prompts of 200..1,500 tokens and 128 generated tokens "
-                         "each through Engine.generate (--steps / 8 timed bursts), tokens/s of wall time")
+                         "each through Engine.generate (--steps / 8 timed bursts), tokens/s of wall time; "
+                         "compare: a Boketar model beside a Falcon-H1 model of equal width, feed-forward size, layer "
+                         "count (--layers, default 4) and vocabulary at --sizes 0.5b or 7b: one prompt step of "
+                         "--prompt-tokens and decode steps of --batch requests at --context, device-timed with the "
+                         "L2 flushed, and the device time of every kernel of one step of each")
     ap.add_argument("--no-check", dest="check", action="store_false",
                     help="skip the comparison with the plain implementation that runs before the timing: the first "
                          "two layers of the run's model, in the run's dtype, on the benchmark's schedule (a "
@@ -502,6 +646,11 @@ def main() -> int:
         args.warmup = 3
     if args.impl == "reference":
         return reference_arm(args)
+    if args.workload == "compare":
+        if args.sizes not in COMPARE_SIZES:
+            print(f"bench.py: --workload compare takes --sizes {' or '.join(sorted(COMPARE_SIZES))}")
+            return 2
+        return compare_workload(args, load_peaks())
 
     import torch
 

@@ -73,6 +73,7 @@ struct DecodeAttnArgs {
   int* split_counter;
   int* status;
   int clustered;          // the key splits of a (sequence, head) are one cluster (gridDim.z blocks)
+  const float* sink;      // [Hq] or nullptr: exp(sink[h]) joins every row's softmax denominator once
 };
 
 // Address of a shared-memory location of this block in block `rank` of the cluster.
@@ -429,6 +430,14 @@ __global__ void __launch_bounds__(kDaThreads)
     const float mu = (mm == -CUDART_INF_F) ? 0.f : mm;
     float ll = 0.f;
     for (int w = 0; w < 4; ++w) ll += s_wl[w][tid] * exp2f(s_wm[w][tid] - mu);
+    if (a.sink != nullptr && z == 0) {
+      // a score without key or value that counts once: it joins the first key range (which may hold
+      // no key: ll is 0 then); maxima are kept in units of log 2
+      const float sk = a.sink[hk * G + tid % G] * 1.4426950408889634f;
+      const float m_new = fmaxf(mm, sk);
+      ll = ll * exp2f(mu - m_new) + exp2f(sk - m_new);
+      mm = m_new;
+    }
     s_M[tid] = mm;
     s_L[tid] = ll;
   }
@@ -631,7 +640,8 @@ PMM_EXPORT int pmm_decode_attention_tma(const void* q_src, long long ldq, const 
                                         const float* inv_freq, void* pool, long long pool_pages, const int* block_table,
                                         int max_blocks, const int* positions, void* out, float* part_o, float* part_ml,
                                         float scale, int window, int split_len, int n_splits, int page_size, int n_seq,
-                                        int Hq, int Hkv, int Dh, int* split_counter, int* status, cudaStream_t stream) {
+                                        int Hq, int Hkv, int Dh, int* split_counter, int* status, const float* sink,
+                                        cudaStream_t stream) {
   if (n_seq <= 0) return 0;
   if (!pmm_decode_attention_tma_supported(Hq, Hkv, Dh, page_size) || !q_src || (k_src == nullptr) != (v_src == nullptr) ||
       !pool || !block_table || !positions || !out || !status || pool_pages <= 0 || !(scale > 0.f) || n_splits < 1 ||
@@ -679,6 +689,7 @@ PMM_EXPORT int pmm_decode_attention_tma(const void* q_src, long long ldq, const 
   a.Hkv = Hkv;
   a.split_counter = split_counter;
   a.status = status;
+  a.sink = sink;
   return Dh == 64 ? pmm::launch_decode_attention<64>(map, a, n_seq, stream)
                   : pmm::launch_decode_attention<128>(map, a, n_seq, stream);
 }

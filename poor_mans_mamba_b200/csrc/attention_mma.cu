@@ -46,6 +46,7 @@ struct FlashDecodeInputs {
   const float* inv_freq;  // [Dh/2], or nullptr: no rotation
   bf16* pool_w;           // the cache, writable
   int one_token;          // tile index == sequence index == token index
+  const float* sink;      // [Hq] or nullptr: exp(sink[h]) joins every row's softmax denominator once
 };
 
 // MT = row tiles of 16 per warp: 1 (64 rows a block) or 2 (128 rows a block, every K/V fragment
@@ -467,7 +468,32 @@ __global__ void __launch_bounds__(128)
     l_hi[mt] += __shfl_xor_sync(0xffffffffu, l_hi[mt], 2);
   }
 
+  // A sink is a score without key or value that counts once: it joins the first key range
+  // (which may hold no key at all).  Maxima are kept in units of log 2.
+  const bool with_sink = dec.sink != nullptr && z == 0;
+  constexpr float kLog2e = 1.4426950408889634f;
   if constexpr (!SPLITW) {
+    if (with_sink) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = row_base + mt * 16 + (half ? r_hi : r_lo);
+          const float sk = dec.sink[hk * G + r % G] * kLog2e;
+          float& m = half ? m_hi[mt] : m_lo[mt];
+          float& l = half ? l_hi[mt] : l_lo[mt];
+          const float m_new = fmaxf(m, sk);
+          const float corr = exp2f(m - m_new);  // no key seen: exp2(-inf) = 0
+          l = l * corr + exp2f(sk - m_new);
+#pragma unroll
+          for (int nt = 0; nt < NT_O; ++nt) {
+            o[mt][nt][half * 2] *= corr;
+            o[mt][nt][half * 2 + 1] *= corr;
+          }
+          m = m_new;
+        }
+      }
+    }
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
@@ -514,6 +540,12 @@ __global__ void __launch_bounds__(128)
       const float mu = (mm == -CUDART_INF_F) ? 0.f : mm;
       float ll = 0.f;
       for (int w = 0; w < 4; ++w) ll += s_wl[w][tid] * exp2f(s_wm[w][tid] - mu);
+      if (with_sink) {
+        const float sk = dec.sink[hk * G + tid % G] * kLog2e;
+        const float m_new = fmaxf(mm, sk);
+        ll = ll * exp2f(mu - m_new) + exp2f(sk - m_new);  // no key seen: ll is 0
+        mm = m_new;
+      }
       s_M[tid] = mm;
       s_L[tid] = ll;
     }
@@ -729,6 +761,7 @@ int flash_dispatch(const void* q, const void* pool, const int* block_table, int 
 
 // tile_rows M: 16 (every sequence brings at most 16/G tokens: decode), 64, or 128 (head sizes
 // up to 64).  n_tiles: number of row tiles = sum over sequences of ceil(new tokens / (M / G)).
+// sink: nullptr, or one float per query head that joins the softmax's denominator as exp(sink[h]).
 // split_counter: nullptr (the caller merges key splits with pmm_flash_combine), or
 // n_tiles*Hkv ints that are zero between calls: then the last block of every tile merges
 // its splits (at most 64 of them) and writes `out` itself.
@@ -737,8 +770,9 @@ PMM_EXPORT int pmm_flash_paged_attention(const void* q, const void* pool, const 
                                          void* out, float* part_o, float* part_ml, float scale,
                                          int window, int split_len, int n_splits, int page_size,
                                          int n_seq, int n_tiles, int tile_rows, int Hq, int Hkv, int Dh,
-                                         int* split_counter, cudaStream_t stream) {
+                                         int* split_counter, const float* sink, cudaStream_t stream) {
   pmm::FlashDecodeInputs dec{};
+  dec.sink = sink;
   return pmm::flash_dispatch(q, pool, block_table, max_blocks, positions, cu, out, part_o, part_ml, scale,
                              window, split_len, n_splits, page_size, n_seq, n_tiles, tile_rows, Hq, Hkv, Dh,
                              split_counter, dec, stream);
@@ -756,7 +790,8 @@ PMM_EXPORT int pmm_flash_decode_attention(const void* q_src, long long ldq, cons
                                           const int* block_table, int max_blocks, const int* positions,
                                           void* out, float* part_o, float* part_ml, float scale, int window,
                                           int split_len, int n_splits, int page_size, int n_seq, int Hq,
-                                          int Hkv, int Dh, int* split_counter, cudaStream_t stream) {
+                                          int Hkv, int Dh, int* split_counter, const float* sink,
+                                          cudaStream_t stream) {
   if (!q_src || (k_src == nullptr) != (v_src == nullptr) || Hkv <= 0 || Hq % Hkv || Hq / Hkv > 16)
     return PMM_ERR_BAD_ARGUMENT;
   if (n_splits > 1 && !split_counter) return PMM_ERR_BAD_ARGUMENT;  // the separate merge is not wired here
@@ -773,6 +808,7 @@ PMM_EXPORT int pmm_flash_decode_attention(const void* q_src, long long ldq, cons
   dec.inv_freq = inv_freq;
   dec.pool_w = static_cast<pmm::bf16*>(pool);
   dec.one_token = 1;
+  dec.sink = sink;
   return pmm::flash_dispatch(nullptr, pool, block_table, max_blocks, positions, nullptr, out, part_o, part_ml,
                              scale, window, split_len, n_splits, page_size, n_seq, n_seq, 16, Hq, Hkv, Dh,
                              split_counter, dec, stream);

@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(kAtThreads, DH == 64 ? 2 : 1)
                         const int* __restrict__ cu, bf16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, float scale_log2, int window, int split_len, int n_splits,
                         int page_size, int n_seq, int Hq, int Hkv, int* __restrict__ split_counter,
-                        int* __restrict__ status) {
+                        int* __restrict__ status, const float* __restrict__ sink) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int NSUB = DH / kAtDhBlock;            // sub-tiles of 64 head-size columns
@@ -382,6 +382,17 @@ __global__ void __launch_bounds__(kAtThreads, DH == 64 ? 2 : 1)
     }
     if (row_ok && alive && !s_abort) {
       const int t = tok0 + row / G, hq = hk * G + row % G;
+      if (sink != nullptr && z == 0) {
+        // a score without key or value that counts once: it joins the first key range (which may
+        // hold no key); maxima are kept in units of log 2
+        const float sk = sink[hq] * 1.4426950408889634f;
+        const float m_new = fmaxf(m_run, sk);
+        const float corr = exp2f(m_run - m_new);
+        l_run = l_run * corr + exp2f(sk - m_new);
+#pragma unroll
+        for (int i = 0; i < DH; ++i) o[i] *= corr;
+        m_run = m_new;
+      }
       if (n_splits == 1) {
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         bf16* dst = out + (static_cast<size_t>(t) * Hq + hq) * DH;
@@ -484,7 +495,7 @@ PMM_EXPORT int pmm_attention_tc(const void* q, const void* pool, long long pool_
                                 int max_blocks, const int* positions, const int* cu, void* out, float* part_o,
                                 float* part_ml, float scale, int window, int split_len, int n_splits, int page_size,
                                 int n_seq, int n_tiles, int Hq, int Hkv, int Dh, int* split_counter, int* status,
-                                cudaStream_t stream) {
+                                const float* sink, cudaStream_t stream) {
   if (n_seq <= 0 || n_tiles <= 0) return 0;
   if (!pmm_attention_tc_supported(Hq, Hkv, Dh, page_size) || !status || !(scale > 0.f) || n_splits < 1 ||
       n_splits > 64 || Hkv > 65535 || pool_pages <= 0 || reinterpret_cast<uintptr_t>(pool) % 16 ||
@@ -514,6 +525,7 @@ PMM_EXPORT int pmm_attention_tc(const void* q, const void* pool, long long pool_
   dim3 grid(n_tiles, Hkv, n_splits);
   pmm::launch_pdl(kern, grid, dim3(pmm::kAtThreads), smem, stream,
       static_cast<const pmm::bf16*>(q), map, block_table, max_blocks, positions, cu, static_cast<pmm::bf16*>(out), part_o,
-      part_ml, scale * 1.4426950408889634f, window, split_len, n_splits, page_size, n_seq, Hq, Hkv, split_counter, status);
+      part_ml, scale * 1.4426950408889634f, window, split_len, n_splits, page_size, n_seq, Hq, Hkv, split_counter, status,
+      sink);
   return pmm::launch_status();
 }

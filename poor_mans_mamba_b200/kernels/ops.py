@@ -76,22 +76,22 @@ _SIGNATURES = {
     "pmm_flash_supported": [c_int, c_int, c_int],
     "pmm_flash_paged_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "pmm_l2_prefetch": [c_void_p, c_void_p, c_int, c_void_p],
     "pmm_attention_tc_supported": [c_int, c_int, c_int, c_int],
     "pmm_attention_tc": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                         c_void_p, c_void_p],
+                         c_void_p, c_void_p, c_void_p],
     "pmm_skinny_chain": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "pmm_flash_decode_attention": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
                                    c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                   c_int, c_void_p, c_void_p],
+                                   c_int, c_void_p, c_void_p, c_void_p],
     "pmm_decode_attention_tma_supported": [c_int, c_int, c_int, c_int],
     "pmm_decode_attention_tma": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float, c_float,
                                  c_float, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                 c_void_p, c_void_p],
+                                 c_void_p, c_void_p, c_void_p],
     "pmm_flash_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_skinny_gemm": [c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int,
                         c_float, c_void_p, c_longlong, c_void_p, c_int, c_float, c_void_p, c_longlong, c_void_p,
@@ -780,7 +780,7 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
                     sink: Optional[Tensor] = None) -> None:
     """Causal attention of every token over keys lo..pos of its request in the paged cache.
     ``sink`` (one float per query head): the softmax's denominator also holds exp(sink[h]), a score
-    without key or value (float kernel only).
+    without key or value.
     With ``cu_seqlens`` and ``new_lens`` (tokens per sequence, host values) a bfloat16 cache of a
     supported shape goes to the tensor-core kernel; everything else to the float kernel.
     ``split_counter`` (int32, zero between calls, at least tiles x kv heads entries) lets the
@@ -811,8 +811,8 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
         part_o = scratch.data_ptr()
         part_ml = part_o + 4 * T * n_q_heads * n_splits * head_dim
     _f32vec(sink, n_q_heads, "attention: sink")
-    flash = (use_tensor_cores and sink is None and q.dtype == torch.bfloat16 and cu_seqlens is not None
-             and new_lens is not None and flash_supported(n_q_heads, n_kv_heads, head_dim))
+    flash = (use_tensor_cores and q.dtype == torch.bfloat16 and cu_seqlens is not None and new_lens is not None
+             and flash_supported(n_q_heads, n_kv_heads, head_dim))
     if flash:
         _i32(cu_seqlens, "attention: cu_seqlens")
         group = n_q_heads // n_kv_heads
@@ -831,7 +831,7 @@ def paged_attention(q: Tensor, pool: Tensor, block_table: Tensor, positions: Ten
         _call("pmm_flash_paged_attention", q.data_ptr(), pool.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], positions.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), part_o,
               part_ml, float(softmax_scale), int(window), int(split_len), int(n_splits), pool.shape[2],
-              len(new_lens), n_tiles, int(tile_rows), n_q_heads, n_kv_heads, head_dim, counter, _stream())
+              len(new_lens), n_tiles, int(tile_rows), n_q_heads, n_kv_heads, head_dim, counter, _ptr(sink), _stream())
         if counter is not None:
             return
     else:
@@ -857,11 +857,14 @@ def flash_decode_attention(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], 
                            v_scale: float, inv_freq: Optional[Tensor], pool: Tensor, block_table: Tensor,
                            positions: Tensor, out: Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
                            softmax_scale: float, window: int = 0, n_splits: int = 1, split_len: int = 0,
-                           scratch: Optional[Tensor] = None, split_counter: Optional[Tensor] = None) -> None:
+                           scratch: Optional[Tensor] = None, split_counter: Optional[Tensor] = None,
+                           sink: Optional[Tensor] = None) -> None:
     """A decode step's attention straight from the projections (token t is sequence t's one new
     token): scales and rotates queries and new keys, writes the new keys and values into their
-    cache pages and attends over the cache, in one launch.  ``k``/``v`` None: the cache has them."""
-    _cuda(q, k, v, inv_freq, pool, block_table, positions, out, scratch, split_counter)
+    cache pages and attends over the cache, in one launch.  ``k``/``v`` None: the cache has them.
+    ``sink``: see paged_attention."""
+    _cuda(q, k, v, inv_freq, pool, block_table, positions, out, scratch, split_counter, sink)
+    _f32vec(sink, n_q_heads, "decode attention: sink")
     n_seq = q.shape[0]
     kv_dim = n_kv_heads * head_dim
     if not (q.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
@@ -904,12 +907,12 @@ def flash_decode_attention(q: Tensor, k: Optional[Tensor], v: Optional[Tensor], 
               float(v_scale), _ptr(inv_freq), pool.data_ptr(), pool.shape[0], block_table.data_ptr(),
               block_table.shape[1], positions.data_ptr(), out.data_ptr(), part_o, part_ml, float(softmax_scale),
               int(window), int(split_len), int(n_splits), pool.shape[2], n_seq, n_q_heads, n_kv_heads, head_dim, counter,
-              _tc_status(q.device).data_ptr(), _stream())
+              _tc_status(q.device).data_ptr(), _ptr(sink), _stream())
         return
     _call("pmm_flash_decode_attention", q.data_ptr(), ldq, _ptr(k), ldk, _ptr(v), ldv, float(q_scale), float(k_scale),
           float(v_scale), _ptr(inv_freq), pool.data_ptr(), block_table.data_ptr(), block_table.shape[1],
           positions.data_ptr(), out.data_ptr(), part_o, part_ml, float(softmax_scale), int(window), int(split_len),
-          int(n_splits), pool.shape[2], n_seq, n_q_heads, n_kv_heads, head_dim, counter, _stream())
+          int(n_splits), pool.shape[2], n_seq, n_q_heads, n_kv_heads, head_dim, counter, _ptr(sink), _stream())
 
 
 SKINNY_MAX_TOKENS = 64  # the weight-streaming products take up to 64 tokens (where their shared memory fits)
@@ -1265,7 +1268,8 @@ def attention_tc_supported(n_q_heads: int, n_kv_heads: int, head_dim: int, page_
 def attention_tc(q: Tensor, pool: Tensor, block_table: Tensor, positions: Tensor, cu_seqlens: Tensor,
                  new_lens: Sequence[int], out: Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
                  softmax_scale: float, window: int = 0, n_splits: int = 1, split_len: int = 0,
-                 scratch: Optional[Tensor] = None, split_counter: Optional[Tensor] = None) -> None:
+                 scratch: Optional[Tensor] = None, split_counter: Optional[Tensor] = None,
+                 sink: Optional[Tensor] = None) -> None:
     """Causal attention of prompt portions over the paged cache on the fifth-generation tensor cores
     (TMA tiles straight from the pages, scores and P V in tensor memory, one thread per query row
     for the softmax).  Same contract as paged_attention with rotated queries and a cache that holds
@@ -1302,7 +1306,7 @@ def attention_tc(q: Tensor, pool: Tensor, block_table: Tensor, positions: Tensor
     _call("pmm_attention_tc", q.data_ptr(), pool.data_ptr(), pool.shape[0], block_table.data_ptr(), block_table.shape[1],
           positions.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), part_o, part_ml, float(softmax_scale), int(window),
           int(split_len), int(n_splits), pool.shape[2], len(new_lens), n_tiles, n_q_heads, n_kv_heads, head_dim, counter,
-          _tc_status(q.device).data_ptr(), _stream())
+          _tc_status(q.device).data_ptr(), _ptr(sink), _stream())
 
 
 def silu_mul(gate_up: Tensor, gate_mult: float, out: Tensor) -> None:

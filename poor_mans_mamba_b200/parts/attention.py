@@ -27,6 +27,54 @@ _TC_FROM_TOKENS = 256   # shorter steps stay on the mma.sync kernel (few 128-row
 _TC_ATTENTION = os.environ.get("PMM_TCGEN05_ATTENTION", "1") == "1"
 
 
+def plan_key_splits_tc(num_heads: int, num_kv_heads: int, window: int, new_lens, kv_len_bound: int):
+    """Key ranges for the tcgen05 kernel (128 rows a block, two blocks an SM): one range when
+    the row tiles alone give a block per SM, else enough ranges of at least 256 keys to get there."""
+    per_tile = 128 // (num_heads // num_kv_heads)
+    blocks = sum((n + per_tile - 1) // per_tile for n in new_lens) * num_kv_heads
+    reach = min(kv_len_bound, window) if window > 0 else kv_len_bound
+    want = min(_TC_BLOCKS // max(blocks, 1), (reach + 255) // 256)
+    if want <= 1:
+        return 1, 0
+    split_len = ((kv_len_bound + want - 1) // want + 63) // 64 * 64
+    n_splits = (kv_len_bound + split_len - 1) // split_len
+    return (n_splits, split_len) if n_splits > 1 else (1, 0)
+
+
+def plan_key_splits(num_heads: int, num_kv_heads: int, head_dim: int, window: int, new_lens, kv_len_bound: int,
+                    dtype: torch.dtype):
+    """How many key ranges every block's keys are cut into: enough blocks to fill the GPU
+    when few tokens are in flight, one when the tokens alone do."""
+    group = num_heads // num_kv_heads
+    if dtype == torch.bfloat16 and K.flash_supported(num_heads, num_kv_heads, head_dim):
+        rows = K.flash_tile_rows(num_heads, num_kv_heads, head_dim, new_lens)
+        per_tile = rows // group
+        blocks = sum((n + per_tile - 1) // per_tile for n in new_lens) * num_kv_heads
+        min_len = 256 if rows == 16 else 64
+        # about two blocks per SM: few warps per block, and causal tiles differ in length; a decode
+        # block of head size 128 fills an SM's shared memory alone, so one block per SM there
+        # (8 requests, 2 KV heads, 4,096 keys: 9 ranges 13.7 us, 17 ranges 21.3 us)
+        target = _TARGET_BLOCKS // 4 if rows == 16 and head_dim > 64 else _TARGET_BLOCKS // 2
+    else:
+        blocks = sum(new_lens) * ((num_heads + 3) // 4)
+        min_len = 128
+        target = _TARGET_BLOCKS
+    reach = min(kv_len_bound, window) if window > 0 else kv_len_bound
+    if blocks >= target or reach <= min_len:
+        return 1, 0
+    if dtype == torch.bfloat16 and min_len == 256:
+        # decode blocks all take the same time: as many as run at once and no more, or a second,
+        # partly filled wave follows (at batch 64: 2 ranges 35 us, 3 ranges 48 us)
+        want = min(max(1, target // blocks), (reach + min_len - 1) // min_len)
+    else:
+        want = min((target + blocks - 1) // blocks, (reach + min_len - 1) // min_len)
+    if want <= 1:
+        return 1, 0
+    split_len = ((kv_len_bound + want - 1) // want + 63) // 64 * 64
+    n_splits = (kv_len_bound + split_len - 1) // split_len
+    return (n_splits, split_len) if n_splits > 1 else (1, 0)
+
+
 class PagedAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: Optional[Dict[str, Any]] = None, in_multiplier: float = 1.0,
@@ -191,49 +239,11 @@ class PagedAttention(Mixer):
                 and K.attention_tc_supported(self.num_heads, self.num_kv_heads, self.head_dim, page_size))
 
     def plan_splits_tc(self, new_lens, kv_len_bound: int):
-        """Key ranges for the tcgen05 kernel (128 rows a block, two blocks an SM): one range when
-        the row tiles alone give a block per SM, else enough ranges of at least 256 keys to get there."""
-        per_tile = 128 // (self.num_heads // self.num_kv_heads)
-        blocks = sum((n + per_tile - 1) // per_tile for n in new_lens) * self.num_kv_heads
-        reach = min(kv_len_bound, self.window) if self.window > 0 else kv_len_bound
-        want = min(_TC_BLOCKS // max(blocks, 1), (reach + 255) // 256)
-        if want <= 1:
-            return 1, 0
-        split_len = ((kv_len_bound + want - 1) // want + 63) // 64 * 64
-        n_splits = (kv_len_bound + split_len - 1) // split_len
-        return (n_splits, split_len) if n_splits > 1 else (1, 0)
+        return plan_key_splits_tc(self.num_heads, self.num_kv_heads, self.window, new_lens, kv_len_bound)
 
     def plan_splits(self, new_lens, kv_len_bound: int, dtype: torch.dtype):
-        """How many key ranges every block's keys are cut into: enough blocks to fill the GPU
-        when few tokens are in flight, one when the tokens alone do."""
-        group = self.num_heads // self.num_kv_heads
-        if dtype == torch.bfloat16 and K.flash_supported(self.num_heads, self.num_kv_heads, self.head_dim):
-            rows = K.flash_tile_rows(self.num_heads, self.num_kv_heads, self.head_dim, new_lens)
-            per_tile = rows // group
-            blocks = sum((n + per_tile - 1) // per_tile for n in new_lens) * self.num_kv_heads
-            min_len = 256 if rows == 16 else 64
-            # about two blocks per SM: few warps per block, and causal tiles differ in length; a decode
-            # block of head size 128 fills an SM's shared memory alone, so one block per SM there
-            # (8 requests, 2 KV heads, 4,096 keys: 9 ranges 13.7 us, 17 ranges 21.3 us)
-            target = _TARGET_BLOCKS // 4 if rows == 16 and self.head_dim > 64 else _TARGET_BLOCKS // 2
-        else:
-            blocks = sum(new_lens) * ((self.num_heads + 3) // 4)
-            min_len = 128
-            target = _TARGET_BLOCKS
-        reach = min(kv_len_bound, self.window) if self.window > 0 else kv_len_bound
-        if blocks >= target or reach <= min_len:
-            return 1, 0
-        if dtype == torch.bfloat16 and min_len == 256:
-            # decode blocks all take the same time: as many as run at once and no more, or a second,
-            # partly filled wave follows (at batch 64: 2 ranges 35 us, 3 ranges 48 us)
-            want = min(max(1, target // blocks), (reach + min_len - 1) // min_len)
-        else:
-            want = min((target + blocks - 1) // blocks, (reach + min_len - 1) // min_len)
-        if want <= 1:
-            return 1, 0
-        split_len = ((kv_len_bound + want - 1) // want + 63) // 64 * 64
-        n_splits = (kv_len_bound + split_len - 1) // split_len
-        return (n_splits, split_len) if n_splits > 1 else (1, 0)
+        return plan_key_splits(self.num_heads, self.num_kv_heads, self.head_dim, self.window, new_lens, kv_len_bound,
+                               dtype)
 
 
 register_mixer("paged_attention", PagedAttention)

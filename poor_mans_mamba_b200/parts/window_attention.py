@@ -21,26 +21,13 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops as K
+from .attention import plan_key_splits, plan_key_splits_tc
 from .base import ParamSpec, StateSpec, register_mixer
 from .recurrent import _StackedInput, causal_conv
 
 Tensor = torch.Tensor
 
-_TARGET_BLOCKS = 592   # the float kernel's key ranges are sized for about this many blocks
-
-
-def plan_key_ranges(n_tokens: int, n_heads: int, kv_len_bound: int, window: int):
-    """(number of key ranges, their length) for the float attention kernel (four heads a block)."""
-    blocks = n_tokens * ((n_heads + 3) // 4)
-    reach = min(kv_len_bound, window) if window > 0 else kv_len_bound
-    if blocks >= _TARGET_BLOCKS or reach <= 128:
-        return 1, 0
-    want = min((_TARGET_BLOCKS + blocks - 1) // blocks, (reach + 127) // 128)
-    if want <= 1:
-        return 1, 0
-    split_len = ((kv_len_bound + want - 1) // want + 63) // 64 * 64
-    n_splits = (kv_len_bound + split_len - 1) // split_len
-    return (n_splits, split_len) if n_splits > 1 else (1, 0)
+_TC_FROM_TOKENS = 256   # shorter steps stay on the mma.sync kernel (few 128-row tiles)
 
 
 class WindowSinkAttention(_StackedInput):
@@ -97,6 +84,10 @@ class WindowSinkAttention(_StackedInput):
             i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
             inv = torch.pow(torch.tensor(self.rot_base, dtype=torch.float64), -2.0 * i / float(self.rot_dims))
             self.inv_freq = inv.to(device=device, dtype=torch.float32).contiguous()
+        # tickets of the key splits (zero between steps): the last block of a tile merges them
+        self._split_counter = torch.zeros(4096, dtype=torch.int32, device=device) if device.type == "cuda" else None
+        if self._split_counter is not None:
+            K.watch_split_counter(self._split_counter)  # cleared if a launch is ever abandoned half-way
 
     def forward_projected(self, proj: Tensor, ctx, cache, out: Tensor) -> None:
         T = proj.shape[0]
@@ -110,16 +101,46 @@ class WindowSinkAttention(_StackedInput):
         K.rope_pairs_store(qkv[:, :self.q_dim], qkv[:, self.q_dim:self.q_dim + self.k_dim],
                            qkv[:, self.q_dim + self.k_dim:], self.inv_freq, self.rot_dims, ctx.positions, ctx.seq_of,
                            kv.block_table, kv.pool, q_rot, self.heads, self.kv_heads, self.dim, self.vdim, Dp)
-        n_splits, split_len = plan_key_ranges(T, self.heads, ctx.kv_len_bound, self.window)
-        scratch = None
-        if n_splits > 1:
-            scratch = ws.alloc((K.attention_scratch_floats(T, self.heads, Dp, n_splits),), torch.float32)
         attn = ws.alloc((T, self.heads * Dp), proj.dtype)
-        K.paged_attention(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.seq_of, attn, self.heads, self.kv_heads,
-                          Dp, self.scale, window=self.window, n_splits=n_splits, split_len=split_len, scratch=scratch,
-                          sink=self.sink)
+        self._attend(q_rot, kv, ctx, attn)
         K.linear(attn, self.w_out, out)
         K.add_row_bias_(out, self.out_bias)
+
+
+    def _attend(self, q_rot: Tensor, kv, ctx, attn: Tensor) -> None:
+        """The step's attention over the pages, which hold the step's keys and values already.  bfloat16
+        runs on the tensor cores where the padded head size is one the kernels take (decode steps: TMA
+        tiles or cp.async gathers; prompt steps of 256 tokens or more: tcgen05; shorter ones:
+        mma.sync); float32, and any other head size, on the float kernel."""
+        T, H, G, Dp, ws = q_rot.shape[0], self.heads, self.kv_heads, self.padded_dim, ctx.workspace
+        counter = self._split_counter
+        bf16 = q_rot.dtype == torch.bfloat16 and counter is not None
+
+        def scratch_for(n_splits):
+            return ws.alloc((K.attention_scratch_floats(T, H, Dp, n_splits),), torch.float32) if n_splits > 1 else None
+
+        if bf16 and ctx.decode_only and K.flash_decode_supported(H, G, Dp):
+            n_splits, split_len = plan_key_splits(H, G, Dp, self.window, ctx.new_lens, ctx.kv_len_bound, q_rot.dtype)
+            if n_splits <= 64 and counter.numel() >= T * G:
+                K.flash_decode_attention(q_rot, None, None, 1.0, 1.0, 1.0, None, kv.pool, kv.block_table, ctx.positions,
+                                         attn, H, G, Dp, self.scale, window=self.window, n_splits=n_splits,
+                                         split_len=split_len, scratch=scratch_for(n_splits), split_counter=counter,
+                                         sink=self.sink)
+                return
+        if (bf16 and not ctx.decode_only and sum(ctx.new_lens) >= _TC_FROM_TOKENS
+                and K.attention_tc_supported(H, G, Dp, kv.pool.shape[2])):
+            n_splits, split_len = plan_key_splits_tc(H, G, self.window, ctx.new_lens, ctx.kv_len_bound)
+            per_tile = 128 // (H // G)
+            tiles = sum((n + per_tile - 1) // per_tile for n in ctx.new_lens)
+            if n_splits <= 64 and counter.numel() >= tiles * G:
+                K.attention_tc(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.cu_seqlens, ctx.new_lens, attn, H, G, Dp,
+                               self.scale, window=self.window, n_splits=n_splits, split_len=split_len,
+                               scratch=scratch_for(n_splits), split_counter=counter, sink=self.sink)
+                return
+        n_splits, split_len = plan_key_splits(H, G, Dp, self.window, ctx.new_lens, ctx.kv_len_bound, q_rot.dtype)
+        K.paged_attention(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.seq_of, attn, H, G, Dp, self.scale,
+                          window=self.window, n_splits=n_splits, split_len=split_len, scratch=scratch_for(n_splits),
+                          cu_seqlens=ctx.cu_seqlens, new_lens=ctx.new_lens, split_counter=counter, sink=self.sink)
 
 
 register_mixer("window_sink_attention", WindowSinkAttention)

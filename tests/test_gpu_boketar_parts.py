@@ -217,6 +217,62 @@ def test_window_edge_and_sink_stand_out(dtype, window):
                 close(one, want[t:t + 1], dtype, f"row {t} alone", f32=2e-5, bf16=3e-2)
 
 
+@pytest.mark.parametrize("window", [40, 64, 65, 200, 0])
+@pytest.mark.parametrize("H,G,Dh", [(4, 2, 64), (8, 1, 64), (2, 2, 128)])
+def test_tensor_core_attention_with_sink_and_window(window, H, G, Dh, monkeypatch):
+    """The same standing-out keys and sinks through every bfloat16 attention kernel: tcgen05 and
+    mma.sync prompt tiles, decode tiles with TMA and with cp.async gathers, one and several key ranges."""
+    dtype, page, T = torch.bfloat16, 64, 330
+    q, k, v = rnd(T, H * Dh, seed=1, scale=0.3), rnd(T, G * Dh, seed=2, scale=0.3), rnd(T, G * Dh, seed=3)
+    qh, kh = q.view(T, H, Dh), k.view(T, G, Dh)
+    w = window if window > 0 else T
+    rep = H // G
+    for i in range(T):
+        for j in (i - w + 1, i - w):
+            if j >= 0 and j != i:
+                kh[j] += qh[i, ::rep] / (qh[i, ::rep].norm(dim=-1, keepdim=True) ** 2) * 2.0
+    k = kh.reshape(T, G * Dh).to(torch.bfloat16).float()
+    sink = torch.linspace(-2.0, 5.0, H)
+    scale = 0.9
+    args = (q.double().view(T, H, Dh), k.double().view(T, G, Dh), v.double().view(T, G, Dh), scale)
+    want = P.windowed_sink_attention(*args, w, sink.double()).reshape(T, H * Dh)
+    if window > 0:
+        assert float((want - P.windowed_sink_attention(*args, w + 1, sink.double()).reshape(T, H * Dh)).abs().max()) > 0.15
+    assert float((want - P.windowed_sink_attention(*args, w, sink.double() - 50.0).reshape(T, H * Dh)).abs().max()) > 0.3
+    n_pages = (T + page - 1) // page
+    pool = torch.zeros(n_pages + 2, 2, page, G * Dh, dtype=dtype, device=DEV)
+    table = torch.tensor([list(range(n_pages, 0, -1))], dtype=torch.int32, device=DEV)
+    qd = torch.empty(T, H * Dh, dtype=dtype, device=DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    seq0 = torch.zeros(T, dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    K.rope_pairs_store(q.to(DEV, dtype), k.to(DEV, dtype), v.to(DEV, dtype), None, 0, pos, seq0, table, pool, qd,
+                       H, G, Dh, Dh, Dh)
+    counter = torch.zeros(4096, dtype=torch.int32, device=DEV)
+    sk = sink.to(DEV)
+    for n_splits, split_len in ((1, 0), (3, 128)):
+        scratch = torch.empty(K.attention_scratch_floats(T, H, Dh, n_splits), device=DEV) if n_splits > 1 else None
+        out = torch.zeros(T, H * Dh, dtype=dtype, device=DEV)
+        K.attention_tc(qd, pool, table, pos, cu, [T], out, H, G, Dh, scale, window=window, n_splits=n_splits,
+                       split_len=split_len, scratch=scratch, split_counter=counter, sink=sk)
+        close(out, want, dtype, f"tcgen05 prompt rows, {n_splits} key ranges", bf16=3e-2)
+        out.zero_()
+        K.paged_attention(qd, pool, table, pos, seq0, out, H, G, Dh, scale, window=window, n_splits=n_splits,
+                          split_len=split_len, scratch=scratch, cu_seqlens=cu, new_lens=[T], split_counter=counter, sink=sk)
+        close(out, want, dtype, f"mma.sync prompt rows, {n_splits} key ranges", bf16=3e-2)
+        for tma in (True, False):
+            monkeypatch.setattr(K, "_TMA_DECODE", tma)
+            for t in (0, 1, w - 1, w, w + 1, 63, 64, 65, 127, 128, T - 1):
+                if 0 <= t < T:
+                    one = torch.zeros(1, H * Dh, dtype=dtype, device=DEV)
+                    K.flash_decode_attention(qd[t:t + 1], None, None, 1.0, 1.0, 1.0, None, pool, table, pos[t:t + 1], one,
+                                             H, G, Dh, scale, window=window, n_splits=n_splits, split_len=split_len,
+                                             scratch=scratch, split_counter=counter, sink=sk)
+                    close(one, want[t:t + 1], dtype, f"decode row {t}, tma {tma}, {n_splits} key ranges", bf16=3e-2)
+    assert int(counter.abs().sum()) == 0
+    K.check_status(DEV, wait=True)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("taps", [1, 2, 3, 5])
 def test_convolution_without_activation_carries_its_window(dtype, taps):
