@@ -71,6 +71,11 @@ _SIGNATURES = {
     "pmm_delta_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
                        c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                        c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
+    "pmm_recurrent_chunked_supported": [c_int, c_int],
+    "pmm_recurrent_chunked_scratch": [c_int, c_int, c_int],
+    "pmm_recurrent_chunked": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
+                              c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
     "pmm_decay_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_flash_supported": [c_int, c_int, c_int],
@@ -1537,6 +1542,59 @@ def decay_scan(q: Tensor, k: Tensor, v: Tensor, decay: Tensor, state: Tensor, cu
     _call("pmm_decay_scan", q.data_ptr(), ld_q, k.data_ptr(), ld_k, v.data_ptr(), ld_v, decay.data_ptr(),
           state.data_ptr(), cu.data_ptr(), slots.data_ptr(), out.data_ptr(), int(n_seq), n_heads, dim, vdim, _dt(q),
           _stream())
+
+
+RECURRENT_CHUNK = 64  # tokens per chunk of the chunked recurrences
+
+
+def recurrent_chunked_supported(dim: int, delta: bool) -> bool:
+    """Whether the chunked kernels take this key size (a multiple of 4 whose operands fit one block)."""
+    return bool(_fn("pmm_recurrent_chunked_supported")(int(dim), int(bool(delta))))
+
+
+def recurrent_chunks(new_lens: Sequence[int]) -> int:
+    return sum((n + RECURRENT_CHUNK - 1) // RECURRENT_CHUNK for n in new_lens)
+
+
+def recurrent_chunked_scratch_floats(new_lens: Sequence[int], n_heads: int, dim: int, vdim: int, delta: bool) -> int:
+    f = _fn("pmm_recurrent_chunked_scratch")
+    f.restype = c_longlong
+    return recurrent_chunks(new_lens) * n_heads * int(f(int(dim), int(vdim), int(bool(delta)))) + 4
+
+
+def recurrent_chunked(q: Tensor, k: Tensor, v: Tensor, state: Tensor, cu: Tensor, slots: Tensor, new_lens: Sequence[int],
+                      out: Tensor, scratch: Tensor, n_heads: int, n_qk_heads: int, dim: int, vdim: int,
+                      decay: Optional[Tensor] = None, beta: Optional[Tensor] = None, a: Optional[Tensor] = None,
+                      dt_bias: Optional[Tensor] = None, a_log: Optional[Tensor] = None, unit_eps: float = 0.0,
+                      q_scale: float = 1.0) -> None:
+    """The recurrences of delta_scan (``decay`` None) and decay_scan (``decay`` given) for prompt portions,
+    in chunks of 64 tokens: one launch prepares every chunk's operands in parallel, a second walks each
+    sequence's chunks in order.  Float arithmetic throughout; same arguments and results (beyond rounding)
+    as the token-serial kernels.  ``new_lens``: tokens per sequence (host values)."""
+    delta = decay is None
+    what = "recurrent_chunked"
+    _cuda(q, k, v, decay, beta, a, dt_bias, a_log, state, cu, slots, out, scratch)
+    T, ld_q, ld_k, ld_v = _recurrent_common(q, k, v, state, cu, slots, out, n_heads, n_qk_heads, dim, vdim, what)
+    if not recurrent_chunked_supported(dim, delta):
+        raise KernelError(f"{what}: key size {dim} is not one the chunked kernels take")
+    ld_b = ld_a = 0
+    if delta:
+        ld_b, ld_a = _rows_view(beta, f"{what}: beta"), _rows_view(a, f"{what}: a")
+        if not (beta.shape == (T, n_heads) and a.shape == (T, n_heads * dim) and beta.dtype == a.dtype == q.dtype):
+            raise KernelError(f"{what}: beta [T, H], a [T, H*d] of q's type")
+        _f32vec(dt_bias, n_heads * dim, f"{what}: dt_bias")
+        _f32vec(a_log, n_heads, f"{what}: a_log")
+    else:
+        _f32vec(decay, n_heads, f"{what}: decay")
+    need = recurrent_chunked_scratch_floats(new_lens, n_heads, dim, vdim, delta)
+    if not (scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need):
+        raise KernelError(f"{what}: needs {need} floats of scratch")
+    base = scratch.data_ptr()
+    base += (-base) % 16
+    _call("pmm_recurrent_chunked", q.data_ptr(), ld_q, k.data_ptr(), ld_k, v.data_ptr(), ld_v, _ptr(beta), ld_b, _ptr(a),
+          ld_a, _ptr(dt_bias), _ptr(a_log), _ptr(decay), state.data_ptr(), cu.data_ptr(), slots.data_ptr(), out.data_ptr(),
+          base, len(new_lens), recurrent_chunks(new_lens), n_heads, n_qk_heads, dim, vdim, float(unit_eps), float(q_scale),
+          _dt(q), _stream())
 
 
 def ensure_built() -> str:

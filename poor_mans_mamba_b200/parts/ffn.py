@@ -55,6 +55,9 @@ class SwiGLU(FeedForward):
         f = self.intermediate_size
         act = ctx.workspace.alloc((T, f), x.dtype)
         tiles = ((T + 255) // 256) * (f // 128)
+        if streaming.swiglu(x, self.gate_up, self.gate_multiplier, act, ctx):
+            streaming.linear(act, self.down, out, ctx)  # a step of few tokens: both products stream their weights
+            return
         if _TC_ENABLED and tiles >= _TC_FROM_TILES and K.tc_gemm_supported(x, self.gate_up, f, True):
             K.tc_gemm_swiglu(x, self.gate_up, self.gate_multiplier, act)
         else:

@@ -16,6 +16,7 @@ from typing import Any, Dict, List, Sequence
 import torch
 
 from ..kernels import ops as K
+from . import streaming
 from . import branches as side_streams
 from .base import Mixer, ParamSpec, PartSpec, StateSpec, build_part, register_mixer
 
@@ -83,7 +84,7 @@ class NormedParallelMixer(Mixer):
         proj = None
         if self._fused is not None:
             proj = ws.alloc((T, self._fused.shape[0]), x.dtype)
-            K.linear(x, self._fused, proj)
+            streaming.linear(x, self._fused, proj, ctx)
         main = torch.cuda.current_stream(x.device)
         side = side_streams.branch_stream(x.device, "mixer") if len(self.mixers) > 1 else None
         for i, m in enumerate(self.mixers):

@@ -23,10 +23,19 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..kernels import ops as K
+from . import streaming
 from . import branches
 from .base import Mixer, ParamSpec, StateSpec, register_mixer
 
 Tensor = torch.Tensor
+
+# Steps whose longest portion has at least this many tokens walk it in chunks (two launches with a
+# fixed cost of tens of microseconds) instead of token by token (about a microsecond a token).
+_CHUNKED_FROM = 32
+
+
+def _chunked(ctx, dim: int, delta: bool) -> bool:
+    return (not ctx.decode_only and max(ctx.new_lens) >= _CHUNKED_FROM and K.recurrent_chunked_supported(dim, delta))
 
 
 class _StackedInput(Mixer):
@@ -44,7 +53,7 @@ class _StackedInput(Mixer):
 
     def forward(self, x: Tensor, ctx, cache, out: Tensor) -> None:
         proj = ctx.workspace.alloc((x.shape[0], self.input_rows()), x.dtype)
-        K.linear(x, self.w_in, proj)
+        streaming.linear(x, self.w_in, proj, ctx)
         self.forward_projected(proj, ctx, cache, out)
 
 
@@ -102,7 +111,8 @@ class GatedDeltaMixer(_StackedInput):
                 StateSpec.fixed("S", (self.heads, self.dim, self.vdim), "float32")]
 
     def bind(self, params: Dict[str, Tensor]) -> None:
-        self.w_in = torch.cat([params["q"], params["k"], params["v"], params["b"], params["a1"], params["g1"]],
+        # the low-rank inputs before the per-head beta: their column blocks then start on 16-byte boundaries
+        self.w_in = torch.cat([params["q"], params["k"], params["v"], params["a1"], params["g1"], params["b"]],
                               dim=0).contiguous()
         self.conv_w = torch.cat([params["q.conv"], params["k.conv"], params["v.conv"]], dim=0).contiguous()
         self.conv_w_t = self.conv_w.t().contiguous()
@@ -115,22 +125,30 @@ class GatedDeltaMixer(_StackedInput):
         T = proj.shape[0]
         ws = ctx.workspace
         c0 = self.conv_dim
-        c1 = c0 + self.heads
-        c2 = c1 + self.decay_rank
-        beta = proj[:, c0:c1]
+        c1 = c0 + self.decay_rank
+        c2 = c1 + self.gate_rank
+        beta = proj[:, c2:c2 + self.heads]
         a = ws.alloc((T, self.heads * self.dim), proj.dtype)
-        K.linear(proj[:, c1:c2], self.a2, a)
+        streaming.linear(proj[:, c0:c1], self.a2, a, ctx)
         gate = ws.alloc((T, self.v_dim), proj.dtype)
-        K.linear(proj[:, c2:c2 + self.gate_rank], self.g2, gate)
+        streaming.linear(proj[:, c1:c2], self.g2, gate, ctx)
         qkv = causal_conv(proj[:, :c0], self.conv_ones, None, self.conv_w, self.conv_w_t,
                           cache.fixed(f"{self.name}.conv"), ctx, activation=True)
         o = ws.alloc((T, self.v_dim), torch.float32)
-        K.delta_scan(qkv[:, :self.qk_dim], qkv[:, self.qk_dim:2 * self.qk_dim], qkv[:, 2 * self.qk_dim:], beta, a,
-                     self.dt_bias, self.a_log, cache.fixed(f"{self.name}.S"), ctx.cu_seqlens, ctx.slots, ctx.n_seq, o,
-                     self.heads, self.kv_heads, self.dim, self.vdim, self.unit_eps, float(self.dim) ** -0.5)
+        q, k, v = qkv[:, :self.qk_dim], qkv[:, self.qk_dim:2 * self.qk_dim], qkv[:, 2 * self.qk_dim:]
+        state = cache.fixed(f"{self.name}.S")
+        if _chunked(ctx, self.dim, True):
+            scratch = ws.alloc((K.recurrent_chunked_scratch_floats(ctx.new_lens, self.heads, self.dim, self.vdim, True),),
+                               torch.float32)
+            K.recurrent_chunked(q, k, v, state, ctx.cu_seqlens, ctx.slots, ctx.new_lens, o, scratch, self.heads,
+                                self.kv_heads, self.dim, self.vdim, beta=beta, a=a, dt_bias=self.dt_bias,
+                                a_log=self.a_log, unit_eps=self.unit_eps, q_scale=float(self.dim) ** -0.5)
+        else:
+            K.delta_scan(q, k, v, beta, a, self.dt_bias, self.a_log, state, ctx.cu_seqlens, ctx.slots, ctx.n_seq, o,
+                         self.heads, self.kv_heads, self.dim, self.vdim, self.unit_eps, float(self.dim) ** -0.5)
         y = ws.alloc((T, self.v_dim), proj.dtype)
         K.gated_norm(o, gate, 1.0, None, self.norm_w, self.norm_eps, self.heads, True, y, gate="sigmoid")
-        K.linear(y, self.w_out, out)
+        streaming.linear(y, self.w_out, out, ctx)
 
 
 class DecayLinearAttention(_StackedInput):
@@ -165,12 +183,19 @@ class DecayLinearAttention(_StackedInput):
         ws = ctx.workspace
         qk, vd = self.qk_dim, self.v_dim
         o = ws.alloc((T, vd), torch.float32)
-        K.decay_scan(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + vd], self.decay,
-                     cache.fixed(f"{self.name}.S"), ctx.cu_seqlens, ctx.slots, ctx.n_seq, o, self.heads, self.dim,
-                     self.vdim)
+        q, k, v = proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + vd]
+        state = cache.fixed(f"{self.name}.S")
+        if _chunked(ctx, self.dim, False):
+            scratch = ws.alloc((K.recurrent_chunked_scratch_floats(ctx.new_lens, self.heads, self.dim, self.vdim, False),),
+                               torch.float32)
+            K.recurrent_chunked(q, k, v, state, ctx.cu_seqlens, ctx.slots, ctx.new_lens, o, scratch, self.heads,
+                                self.heads, self.dim, self.vdim, decay=self.decay)
+        else:
+            K.decay_scan(q, k, v, self.decay, state, ctx.cu_seqlens, ctx.slots, ctx.n_seq, o, self.heads, self.dim,
+                         self.vdim)
         y = ws.alloc((T, vd), proj.dtype)
         K.gated_norm(o, proj[:, 2 * qk + vd:], 1.0, None, self.norm_w, self.norm_eps, 1, True, y, gate="sigmoid")
-        K.linear(y, self.w_out, out)
+        streaming.linear(y, self.w_out, out, ctx)
 
 
 register_mixer("gated_delta", GatedDeltaMixer)

@@ -12,6 +12,12 @@ against three operations:
     normed_swiglu(h, norm, gate_up, gate_mult, out, ctx) out = silu(g * gate_mult) * u,  [g | u] = norm(h) @ gate_up^T
     add_products(h, [(x, w, scale), ...], ctx)          h += sum scale * x @ w^T        (one or two products)
 
+and, for parts whose input is no residual stream (a mixer's inner projections, a feed-forward that
+is handed normed rows):
+
+    linear(x, w, out, ctx)                              out = x @ w^T
+    swiglu(x, gate_up, gate_mult, out, ctx)             out = silu(g * gate_mult) * u,  [g | u] = x @ gate_up^T
+
 h is the float32 residual stream [T, D]; x, w and out are bfloat16.
 """
 from __future__ import annotations
@@ -85,3 +91,33 @@ def add_products(h: Tensor, products: Sequence[Tuple[Tensor, Tensor, float]], ct
         K.skinny_tc_residual(h, products)
     else:
         K.skinny_residual(h, products)
+
+
+def _streams(x: Tensor, w: Tensor, out: Tensor, ctx) -> bool:
+    """Whether a product of these operands may take the weight-streaming kernels."""
+    return (eligible(ctx, x.shape[1]) and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous() and w.data_ptr() % 16 == 0
+            and out.stride(1) == 1 and out.dtype == torch.bfloat16)
+
+
+def linear(x: Tensor, w: Tensor, out: Tensor, ctx) -> None:
+    """out = x @ w^T: the weight-streaming product in steps of few tokens, else the library product."""
+    if _streams(x, w, out, ctx):
+        if _tensor_core(x.shape[0]) and K.skinny_tc_supported("store", x, w, out):
+            K.skinny_tc_linear(x, w, out)
+        else:
+            K.skinny_linear(x, w, out)
+    else:
+        K.linear(x, w, out)
+
+
+def swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor, ctx) -> bool:
+    """out = silu(g * gate_mult) * u with [g | u] = x @ gate_up^T in one weight-streaming launch; False
+    (nothing done) where the step or the operands do not allow it."""
+    if not _streams(x, gate_up, out, ctx):
+        return False
+    if _tensor_core(x.shape[0]) and K.skinny_tc_supported("swiglu", x, gate_up, out):
+        K.skinny_tc_swiglu(x, gate_up, gate_mult, out)
+    else:
+        K.skinny_swiglu(x, gate_up, gate_mult, out)
+    return True

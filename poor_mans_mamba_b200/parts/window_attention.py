@@ -21,6 +21,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops as K
+from . import streaming
 from .attention import plan_key_splits, plan_key_splits_tc
 from .base import ParamSpec, StateSpec, register_mixer
 from .recurrent import _StackedInput, causal_conv
@@ -103,7 +104,7 @@ class WindowSinkAttention(_StackedInput):
                            kv.block_table, kv.pool, q_rot, self.heads, self.kv_heads, self.dim, self.vdim, Dp)
         attn = ws.alloc((T, self.heads * Dp), proj.dtype)
         self._attend(q_rot, kv, ctx, attn)
-        K.linear(attn, self.w_out, out)
+        streaming.linear(attn, self.w_out, out, ctx)
         K.add_row_bias_(out, self.out_bias)
 
 

@@ -138,6 +138,83 @@ def test_decayed_linear_attention_far_back(dtype, H, d, dv):
     assert float(state[0].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,G,d,dv", [(4, 2, 24, 16), (2, 2, 64, 40), (3, 1, 128, 96), (1, 1, 8, 8), (2, 1, 192, 33)])
+def test_gated_delta_rule_in_chunks(dtype, H, G, d, dv):
+    """Sequences of 1, 63, 64, 65 and 200 tokens (chunk edges), the longest cut into two steps at an odd
+    place, strong and weak decays side by side: the chunked kernels against the plain recurrence and
+    against the token-serial kernel, state included."""
+    lens = [200, 1, 63, 64, 65]
+    T = sum(lens)
+    q, k, v = rnd(T, G * d, seed=1), rnd(T, G * d, seed=2), rnd(T, H * dv, seed=3)
+    beta, a = rnd(T, H, seed=4), rnd(T, H * d, seed=5, scale=3.0)
+    dt_bias, a_log = rnd(H * d, seed=6) - 1.0, rnd(H, seed=7) * 0.5 + 1.0   # decays from 1 down to e^-12 a token
+    g = torch.exp(-torch.exp(a_log.double())[None, :, None] * P.softplus(a.double() + dt_bias.double()).view(T, H, d))
+    assert float(g.min()) < 1e-3 and float(g.max()) > 0.99
+    qd, kd = q.double().view(T, G, d), k.double().view(T, G, d)
+    qn = (qd / torch.sqrt((qd * qd).sum(-1, keepdim=True) + 1e-6) * d ** -0.5).repeat_interleave(H // G, dim=1)
+    kn = (kd / torch.sqrt((kd * kd).sum(-1, keepdim=True) + 1e-6)).repeat_interleave(H // G, dim=1)
+    want, t0 = [], 0
+    for n in lens:
+        sl = slice(t0, t0 + n)
+        want.append(P.gated_delta_rule(qn[sl], kn[sl], v.double().view(T, H, dv)[sl], torch.sigmoid(beta.double())[sl], g[sl]))
+        t0 += n
+    want = torch.cat(want).reshape(T, H * dv)
+    dev = lambda t: t.to(DEV, dtype)
+    slots = [4, 0, 2, 1, 3]
+    results = {}
+    for kind in ("chunked", "serial"):
+        state = torch.zeros(6, H, d, dv, device=DEV)
+        out = torch.empty(T, H * dv, device=DEV)
+        first = [77, 1, 63, 64, 65]
+        starts = [0, 200, 201, 264, 328]
+        for part in (0, 1):
+            rows, ls, sl = [], [], []
+            for i, n in enumerate(lens):
+                lo, hi = (0, first[i]) if part == 0 else (first[i], n)
+                if hi > lo:
+                    rows += list(range(starts[i] + lo, starts[i] + hi))
+                    ls.append(hi - lo)
+                    sl.append(slots[i])
+            idx = torch.tensor(rows)
+            cu, _, sl_t = batch_index(ls, sl)
+            o = torch.empty(len(rows), H * dv, device=DEV)
+            if kind == "chunked":
+                scratch = torch.empty(K.recurrent_chunked_scratch_floats(ls, H, d, dv, True), device=DEV)
+                K.recurrent_chunked(dev(q[idx]), dev(k[idx]), dev(v[idx]), state, cu, sl_t, ls, o, scratch, H, G, d, dv,
+                                    beta=dev(beta[idx]), a=dev(a[idx]), dt_bias=dt_bias.to(DEV), a_log=a_log.to(DEV),
+                                    unit_eps=1e-6, q_scale=d ** -0.5)
+            else:
+                K.delta_scan(dev(q[idx]), dev(k[idx]), dev(v[idx]), dev(beta[idx]), dev(a[idx]), dt_bias.to(DEV),
+                             a_log.to(DEV), state, cu, sl_t, len(ls), o, H, G, d, dv, 1e-6, d ** -0.5)
+            out[idx.to(DEV)] = o
+        close(out, want, torch.float32, f"delta rule, {kind}", f32=1e-4)
+        results[kind] = state
+    close(results["chunked"], results["serial"].cpu(), torch.float32, "states", f32=1e-4)
+    assert float(results["chunked"][5].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,d,dv", [(2, 16, 24), (4, 32, 32), (1, 100, 7), (3, 4, 130)])
+def test_decayed_linear_attention_in_chunks(dtype, H, d, dv):
+    T = 600
+    q, k, v = rnd(T, H * d, seed=1), rnd(T, H * d, seed=2), rnd(T, H * dv, seed=3)
+    decay = [1.0] + [0.97, 0.5, 0.0][:H - 1]
+    want = P.decayed_linear_attention(P.silu(q.double()).view(T, H, d), P.silu(k.double()).view(T, H, d),
+                                      P.silu(v.double()).view(T, H, dv), decay).reshape(T, H * dv)
+    state = torch.zeros(2, H, d, dv, device=DEV)
+    out = torch.empty(T, H * dv, device=DEV)
+    t0 = 0
+    for n in [1, 65, 64, 270, 200]:
+        cu, _, sl = batch_index([n], [1])
+        scratch = torch.empty(K.recurrent_chunked_scratch_floats([n], H, d, dv, False), device=DEV)
+        K.recurrent_chunked(q[t0:t0 + n].to(DEV, dtype), k[t0:t0 + n].to(DEV, dtype), v[t0:t0 + n].to(DEV, dtype), state,
+                            cu, sl, [n], out[t0:t0 + n], scratch, H, H, d, dv, decay=torch.tensor(decay, device=DEV))
+        t0 += n
+    close(out, want, torch.float32, "decayed linear attention in chunks", f32=1e-4)
+    assert float(state[0].abs().max()) == 0.0
+
+
 # ----------------------------------------------------------------------------- window attention pieces
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,d,dv,rot", [(4, 2, 16, 32, 8), (2, 2, 48, 48, 48), (3, 1, 64, 16, 0), (8, 4, 64, 48, 64)])
