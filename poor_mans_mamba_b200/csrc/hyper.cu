@@ -9,7 +9,7 @@
 // the lanes are left alone and only the listed rows are normed (the model's last norm).
 // Everything is float arithmetic; y and the normed rows have the storage type.
 //
-// normed_sum: out = scale * sum_b rmsnorm(x_b) * w_b for up to four branches of one width.
+// normed_sum: out = scale * sum_b rmsnorm(x_b + bias_b) * w_b for up to four branches of one width.
 #include "common.cuh"
 
 namespace pmm {
@@ -17,7 +17,8 @@ namespace pmm {
 constexpr int kMaxLanes = 8;
 constexpr int kMaxBranches = 4;
 
-template <typename S, typename Y>
+// NL: an upper bound of the lane count that sizes the registers (2, 4 or 8)
+template <typename S, typename Y, bool VEC, int NL>
 __global__ void __launch_bounds__(256)
     hc_mix_norm_kernel(const float* x_in, long long in_lane_stride, float* x_out,
                        long long out_lane_stride, int n_lanes, const Y* __restrict__ y,
@@ -38,40 +39,70 @@ __global__ void __launch_bounds__(256)
   const int r = blockIdx.x;
   const int t = rows ? rows[r] : r;
   float ss = 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float xo[kMaxLanes], xn[kMaxLanes];
-#pragma unroll
-    for (int s = 0; s < kMaxLanes; ++s)
-      if (s < n_lanes) xo[s] = x_in[s * in_lane_stride + static_cast<long long>(t) * D + d];
+  const bool write_lanes = x_out && !rows && (y || x_out != x_in || in_lane_stride != out_lane_stride);
+  // one element of every lane at a time; four neighbouring ones (16-byte accesses) where VEC is set
+  auto element = [&](int d, const float* xo, float yv, float* xn) {
     if (y) {
-      const float yv = ldf(y + static_cast<size_t>(t) * D + d);
 #pragma unroll
-      for (int to = 0; to < kMaxLanes; ++to) {
+      for (int to = 0; to < NL; ++to) {
         if (to < n_lanes) {
           float a = 0.f;
 #pragma unroll
-          for (int s = 0; s < kMaxLanes; ++s)
+          for (int s = 0; s < NL; ++s)
             if (s < n_lanes) a += s_mix[s * n_lanes + to] * xo[s];
           xn[to] = a + s_out[to] * yv;
         }
       }
     } else {
 #pragma unroll
-      for (int s = 0; s < kMaxLanes; ++s)
+      for (int s = 0; s < NL; ++s)
         if (s < n_lanes) xn[s] = xo[s];
-    }
-    if (x_out && !rows && (y || x_out != x_in || in_lane_stride != out_lane_stride)) {
-#pragma unroll
-      for (int s = 0; s < kMaxLanes; ++s)
-        if (s < n_lanes) x_out[s * out_lane_stride + static_cast<long long>(t) * D + d] = xn[s];
     }
     if (normed) {
       float u = 0.f;
 #pragma unroll
-      for (int s = 0; s < kMaxLanes; ++s)
+      for (int s = 0; s < NL; ++s)
         if (s < n_lanes) u += s_in[s] * xn[s];
       u_row[d] = u;
       ss += u * u;
+    }
+  };
+  if (VEC) {
+    for (int d = threadIdx.x * 4; d < D; d += blockDim.x * 4) {
+      float xo[4][NL], xn[4][NL], yv[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < NL; ++s) {
+        if (s < n_lanes) {
+          const float4 v = *reinterpret_cast<const float4*>(x_in + s * in_lane_stride + static_cast<long long>(t) * D + d);
+          xo[0][s] = v.x; xo[1][s] = v.y; xo[2][s] = v.z; xo[3][s] = v.w;
+        }
+      }
+      if (y) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) yv[e] = ldf(y + static_cast<size_t>(t) * D + d + e);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) element(d + e, xo[e], yv[e], xn[e]);
+      if (write_lanes) {
+#pragma unroll
+        for (int s = 0; s < NL; ++s)
+          if (s < n_lanes)
+            *reinterpret_cast<float4*>(x_out + s * out_lane_stride + static_cast<long long>(t) * D + d) =
+                make_float4(xn[0][s], xn[1][s], xn[2][s], xn[3][s]);
+      }
+    }
+  } else {
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      float xo[NL], xn[NL];
+#pragma unroll
+      for (int s = 0; s < NL; ++s)
+        if (s < n_lanes) xo[s] = x_in[s * in_lane_stride + static_cast<long long>(t) * D + d];
+      element(d, xo, y ? ldf(y + static_cast<size_t>(t) * D + d) : 0.f, xn);
+      if (write_lanes) {
+#pragma unroll
+        for (int s = 0; s < NL; ++s)
+          if (s < n_lanes) x_out[s * out_lane_stride + static_cast<long long>(t) * D + d] = xn[s];
+      }
     }
   }
   if (!normed) return;
@@ -85,6 +116,7 @@ struct Branches {
   const void* x[kMaxBranches];
   long long ld[kMaxBranches];
   const float* w[kMaxBranches];
+  const float* bias[kMaxBranches];  // added to the branch before its norm, or nullptr
 };
 
 template <typename S, typename O>
@@ -101,7 +133,7 @@ __global__ void __launch_bounds__(256)
       const S* x = static_cast<const S*>(b.x[i]) + static_cast<long long>(t) * b.ld[i];
       float ss = 0.f;
       for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        const float v = ldf(x + d);
+        const float v = ldf(x + d) + (b.bias[i] ? b.bias[i][d] : 0.f);
         ss += v * v;
       }
       inv[i] = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(D) + eps);
@@ -111,7 +143,9 @@ __global__ void __launch_bounds__(256)
     float a = 0.f;
 #pragma unroll
     for (int i = 0; i < kMaxBranches; ++i)
-      if (i < n) a += ldf(static_cast<const S*>(b.x[i]) + static_cast<long long>(t) * b.ld[i] + d) * inv[i] * b.w[i][d];
+      if (i < n)
+        a += (ldf(static_cast<const S*>(b.x[i]) + static_cast<long long>(t) * b.ld[i] + d) + (b.bias[i] ? b.bias[i][d] : 0.f)) *
+             inv[i] * b.w[i][d];
     stf(out + static_cast<size_t>(t) * D + d, a * scale);
   }
 }
@@ -131,8 +165,14 @@ PMM_EXPORT int pmm_hc_mix_norm(const float* x_in, long long in_lane_stride, floa
   if (normed && (!in_w || !norm_w)) return PMM_ERR_BAD_ARGUMENT;
   const size_t smem = normed ? static_cast<size_t>(D) * sizeof(float) : 0;
   if (smem > 200 * 1024) return PMM_ERR_BAD_ARGUMENT;
+  // 16-byte accesses where every row of every lane starts on such a boundary
+  const bool vec = D % 4 == 0 && reinterpret_cast<uintptr_t>(x_in) % 16 == 0 && in_lane_stride % 4 == 0 &&
+                   (!x_out || (reinterpret_cast<uintptr_t>(x_out) % 16 == 0 && out_lane_stride % 4 == 0));
   PMM_DISPATCH_DTYPE(dtype, S, PMM_DISPATCH_DTYPE(y_dtype, Y, {
-    auto kern = pmm::hc_mix_norm_kernel<S, Y>;
+    auto kern = vec ? (n_lanes <= 2 ? pmm::hc_mix_norm_kernel<S, Y, true, 2>
+                                    : n_lanes <= 4 ? pmm::hc_mix_norm_kernel<S, Y, true, 4> : pmm::hc_mix_norm_kernel<S, Y, true, 8>)
+                    : (n_lanes <= 2 ? pmm::hc_mix_norm_kernel<S, Y, false, 2>
+                                    : n_lanes <= 4 ? pmm::hc_mix_norm_kernel<S, Y, false, 4> : pmm::hc_mix_norm_kernel<S, Y, false, 8>);
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
       if (e != cudaSuccess) return static_cast<int>(e);
@@ -143,9 +183,11 @@ PMM_EXPORT int pmm_hc_mix_norm(const float* x_in, long long in_lane_stride, floa
   return pmm::launch_status();
 }
 
-// x[i]: [T, D] rows of stride ld[i] in the storage type; w[i]: [D] floats; out [T, D] contiguous, float when
+// x[i]: [T, D] rows of stride ld[i] in the storage type; w[i]: [D] floats; bias: nullptr, or per branch [D]
+// floats (or nullptr) added to the branch before its norm; out [T, D] contiguous, float when
 // out_f32 is set, else the storage type.
-PMM_EXPORT int pmm_normed_sum(const void* const* x, const long long* ld, const float* const* w, int n, float eps,
+PMM_EXPORT int pmm_normed_sum(const void* const* x, const long long* ld, const float* const* w,
+                              const float* const* bias, int n, float eps,
                               float scale, void* out, int out_f32, int T, int D, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (n < 1 || n > pmm::kMaxBranches || D <= 0) return PMM_ERR_BAD_ARGUMENT;
@@ -154,6 +196,7 @@ PMM_EXPORT int pmm_normed_sum(const void* const* x, const long long* ld, const f
     b.x[i] = x[i];
     b.ld[i] = ld[i];
     b.w[i] = w[i];
+    b.bias[i] = bias ? bias[i] : nullptr;
   }
   PMM_DISPATCH_DTYPE(dtype, S, {
     if (out_f32)

@@ -18,7 +18,8 @@
 // Only differences L_i - L_j with i >= j are ever exponentiated, so nothing overflows however strong
 // the decay.  Two launches: `chunk_prepare` makes W, Uv, B, Q * exp L, K * exp(L_end - L) and exp L_end
 // for every (chunk, head) in parallel; `chunk_apply` walks each sequence's chunks in order, a block per
-// (sequence, head, 16 state columns), with three small matrix products per chunk.  All arithmetic is
+// (sequence, head, 16 state columns), with three small matrix products per chunk and the next chunk's
+// operands fetched meanwhile.  All arithmetic is
 // float on the CUDA cores: scores, decays, the triangular solve and the state stay 32-bit in both
 // storage types.  Chunks start at the portion's first token; results do not depend on where a
 // portion is cut beyond rounding.
@@ -27,9 +28,8 @@
 namespace pmm {
 
 constexpr int kChunk = 64;
-constexpr int kPrepThreads = 256;
-constexpr int kApplyThreads = 128;
-constexpr int kApplyCols = 16;
+constexpr int kPrepThreads = 512;
+constexpr int kApplyThreads = 256;
 
 __device__ __forceinline__ float sigmoid_c(float x) { return 1.f / (1.f + expf(-x)); }
 
@@ -182,38 +182,65 @@ __global__ void __launch_bounds__(kPrepThreads)
   }
   __syncthreads();  // A is whole; q is no longer needed: its rows become the right-hand sides
 
-  // ---- T X = diag(beta) R by forward substitution, a thread per column, d columns at a time:
-  //      first R = K * exp L (X = W), then R = V (X = Uv)
-  float* sX = sQ;
-  const int n_cols = d + dv;
-  for (int c0 = 0; c0 < n_cols; c0 += d) {
-    const bool is_w = c0 == 0;
-    const int width = is_w ? d : min(d, n_cols - c0);
-    for (int c = tid; c < width; c += kPrepThreads) {
+  // ---- T X = diag(beta) R by forward substitution in place, a thread per column.  R = K * exp L
+  //      (X = W) lies where q was; R = V (X = Uv), d columns at a time, where the logarithms were:
+  //      they are no longer needed once K * exp L is made.
+  float* sXw = sQ;
+  float* sXv = sL;
+  for (int e = tid; e < n * d; e += kPrepThreads) {
+    const int i = e / d, c = e - i * d;
+    sXw[i * ds + c] = sK[i * ds + c] * expf(sL[i * ds + c]);
+  }
+  __syncthreads();
+  for (int v0 = 0; v0 < dv; v0 += d) {
+    const int vw = min(d, dv - v0);
+    for (int e = tid; e < n * vw; e += kPrepThreads) {
+      const int i = e / vw, c = e - i * vw;
+      sXv[i * ds + c] = ldf(gv + static_cast<long long>(t0 + i) * p.ld_v + h * dv + v0 + c);
+    }
+    __syncthreads();
+    const int n_cols = (v0 == 0 ? d : 0) + vw;  // the first pass also solves for W
+    for (int col = tid; col < n_cols; col += kPrepThreads) {
+      const bool is_w = v0 == 0 && col < d;
+      const int c = is_w ? col : col - (v0 == 0 ? d : 0);
+      float* x = (is_w ? sXw : sXv) + c;
       for (int j = 0; j < n; ++j) {
-        float r;
-        if (is_w) {
-          r = sK[j * ds + c] * expf(sL[j * ds + c]);
-        } else {
-          r = ldf(gv + static_cast<long long>(t0 + j) * p.ld_v + h * dv + (c0 - d) + c);
-        }
         const float* arow = sA + j * (kChunk + 1);
-        float acc = 0.f;
-        for (int m = 0; m < j; ++m) acc += arow[m] * sX[m * ds + c];
-        const float x = s_beta[j] * (r - acc);
-        sX[j * ds + c] = x;
-        if (is_w) oW[j * d + c] = x;
-        else oUv[j * dv + (c0 - d) + c] = x;
+        float acc0 = 0.f, acc1 = 0.f;
+        int m = 0;
+        for (; m + 1 < j; m += 2) {
+          acc0 += arow[m] * x[m * ds];
+          acc1 += arow[m + 1] * x[(m + 1) * ds];
+        }
+        if (m < j) acc0 += arow[m] * x[m * ds];
+        const float xj = s_beta[j] * (x[j * ds] - (acc0 + acc1));
+        x[j * ds] = xj;
+        if (is_w) oW[j * d + c] = xj;
+        else oUv[j * dv + v0 + c] = xj;
       }
     }
-    // a column is read and written by one thread only: no barrier between the passes
+    __syncthreads();  // the next pass loads further columns of V over these
   }
 }
 
-// Rows of S owned by a thread in the state update: RPT consecutive rows, d <= 8 * RPT.
-template <int RPT, bool DELTA>
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src) {
+  const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// A block owns NC (16, or 8 where that is needed to fill the GPU) columns of one head's state for one
+// sequence and walks the sequence's chunks in order.  Thread (column c, row group rg of 256 / NC): rows
+// rg * NC/4 .. of the chunk in the products with S, rows rg * RPT .. + RPT - 1 of S in the state update
+// (d <= RPT * 256 / NC).  The next chunk's
+// operands come by asynchronous copies while this chunk is computed: Q * exp L and W as soon as the
+// products with S are done, B, K * exp(L_end - L) and Uv once the state update has read them.
+template <int NC, int RPT, bool DELTA>
 __global__ void __launch_bounds__(kApplyThreads)
     chunk_apply_kernel(ChunkArgs p) {
+  constexpr int kRows = kChunk / (kApplyThreads / NC);  // rows of a chunk per thread in the products with S
   extern __shared__ __align__(16) float sm[];
   const int d = p.d, dv = p.dv;
   float* sW = sm;                          // [C][d]   (delta)
@@ -221,57 +248,78 @@ __global__ void __launch_bounds__(kApplyThreads)
   float* sQg = sKe + kChunk * d;           // [C][d]
   float* sB = sQg + kChunk * d;            // [C][C]
   float* sU = sB + kChunk * kChunk;        // [C][NC]
-  float* sS = sU + kChunk * kApplyCols;    // [d][NC]
-  float* sEg = sS + d * kApplyCols;        // [d]
+  float* sS = sU + kChunk * NC;    // [d][NC]
+  float* sEg = sS + d * NC;        // [d]
   pdl_launch_dependents();
   pdl_wait();
-  const int seq = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * kApplyCols;
+  const int seq = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * NC;
   const int tid = threadIdx.x;
-  const int c = tid % kApplyCols, rg = tid / kApplyCols;  // column, row group (8 of them)
+  const int c = tid % NC, rg = tid / NC;
   const int first = p.cu[seq], len = p.cu[seq + 1] - first;
   if (len <= 0) return;
-  int chunk = 0;
-  for (int s = 0; s < seq; ++s) chunk += (p.cu[s + 1] - p.cu[s] + kChunk - 1) / kChunk;
+  int chunk0 = 0;
+  for (int s = 0; s < seq; ++s) chunk0 += (p.cu[s + 1] - p.cu[s] + kChunk - 1) / kChunk;
   const bool col_ok = j0 + c < dv;
+  const bool tile_async = dv % 4 == 0;
+  const int d4 = d / 4;
   float* st = p.state + ((static_cast<size_t>(p.slots[seq]) * p.H + h) * d) * dv;
-  for (int e = tid; e < d * kApplyCols; e += kApplyThreads) {
-    const int r = e / kApplyCols, cc = e % kApplyCols;
+
+  auto fetch_early = [&](int chunk, int n) {   // operands of the products with S
+    const size_t ch = static_cast<size_t>(chunk) * p.H + h;
+    const float* gQg = p.Qg + ch * kChunk * d;
+    for (int e = tid; e < n * d4; e += kApplyThreads) cp_async16(sQg + 4 * e, gQg + 4 * e);
+    if (DELTA) {
+      const float* gW = p.W + ch * kChunk * d;
+      for (int e = tid; e < n * d4; e += kApplyThreads) cp_async16(sW + 4 * e, gW + 4 * e);
+    }
+    cp_async_commit();
+  };
+  auto fetch_late = [&](int chunk, int n) {    // the rest
+    const size_t ch = static_cast<size_t>(chunk) * p.H + h;
+    const float* gKe = p.Ke + ch * kChunk * d;
+    for (int e = tid; e < n * d4; e += kApplyThreads) cp_async16(sKe + 4 * e, gKe + 4 * e);
+    const float* gB = p.B + ch * kChunk * kChunk;
+    for (int e = tid; e < n * (kChunk / 4); e += kApplyThreads) cp_async16(sB + 4 * e, gB + 4 * e);
+    const float* gU = p.Uv + ch * kChunk * dv;
+    if (tile_async) {
+      for (int e = tid; e < n * (NC / 4); e += kApplyThreads) {
+        const int i = e / (NC / 4), g = e % (NC / 4);
+        if (j0 + 4 * g < dv) cp_async16(sU + i * NC + 4 * g, gU + static_cast<size_t>(i) * dv + j0 + 4 * g);
+        else *reinterpret_cast<float4*>(sU + i * NC + 4 * g) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    } else {
+      for (int e = tid; e < n * NC; e += kApplyThreads) {
+        const int i = e / NC, cc = e % NC;
+        sU[e] = (j0 + cc < dv) ? gU[static_cast<size_t>(i) * dv + j0 + cc] : 0.f;
+      }
+    }
+    for (int e = tid; e < d4; e += kApplyThreads) cp_async16(sEg + 4 * e, p.Eg + ch * d + 4 * e);
+    cp_async_commit();
+  };
+
+  fetch_early(chunk0, min(kChunk, len));
+  fetch_late(chunk0, min(kChunk, len));
+  for (int e = tid; e < d * NC; e += kApplyThreads) {
+    const int r = e / NC, cc = e % NC;
     sS[e] = (j0 + cc < dv) ? st[static_cast<size_t>(r) * dv + j0 + cc] : 0.f;
   }
-  const int d4 = d / 4;
+  int chunk = chunk0;
   for (int t0 = 0; t0 < len; t0 += kChunk, ++chunk) {
     const int n = min(kChunk, len - t0);
-    const size_t ch = static_cast<size_t>(chunk) * p.H + h;
-    __syncthreads();  // the chunk before is done with the operands
-    {  // operands of this chunk: whole rows, 16 bytes a thread
-      const float4* gKe = reinterpret_cast<const float4*>(p.Ke + ch * kChunk * d);
-      const float4* gQg = reinterpret_cast<const float4*>(p.Qg + ch * kChunk * d);
-      const float4* gW = DELTA ? reinterpret_cast<const float4*>(p.W + ch * kChunk * d) : nullptr;
-      for (int e = tid; e < n * d4; e += kApplyThreads) {
-        reinterpret_cast<float4*>(sKe)[e] = gKe[e];
-        reinterpret_cast<float4*>(sQg)[e] = gQg[e];
-        if (DELTA) reinterpret_cast<float4*>(sW)[e] = gW[e];
-      }
-      const float4* gB = reinterpret_cast<const float4*>(p.B + ch * kChunk * kChunk);
-      for (int e = tid; e < n * (kChunk / 4); e += kApplyThreads) reinterpret_cast<float4*>(sB)[e] = gB[e];
-      const float* gU = p.Uv + ch * kChunk * dv;
-      for (int e = tid; e < n * kApplyCols; e += kApplyThreads) {
-        const int i = e / kApplyCols, cc = e % kApplyCols;
-        sU[e] = (j0 + cc < dv) ? gU[i * dv + j0 + cc] : 0.f;
-      }
-      for (int e = tid; e < d; e += kApplyThreads) sEg[e] = p.Eg[ch * d + e];
-    }
-    __syncthreads();
-    // ---- rows i = rg * 8 .. rg * 8 + 7 of U = Uv - W S and of the read-out's first term Qg S
-    float o[8], u[8];
+    const bool more = t0 + kChunk < len;
+    const int n_next = more ? min(kChunk, len - t0 - kChunk) : 0;
+    cp_async_wait<1>();  // Q * exp L and W of this chunk have landed (the later group may still fly)
+    __syncthreads();     // ... for every thread, and everyone's rows of S are written
+    // ---- rows i = rg * 4 .. + 3 of W S and of the read-out's first term (Q * exp L) S
+    float o[kRows], u[kRows];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) o[r] = u[r] = 0.f;
+    for (int r = 0; r < kRows; ++r) o[r] = u[r] = 0.f;
     for (int k4 = 0; k4 < d4; ++k4) {
-      const float s0 = sS[(4 * k4 + 0) * kApplyCols + c], s1 = sS[(4 * k4 + 1) * kApplyCols + c];
-      const float s2 = sS[(4 * k4 + 2) * kApplyCols + c], s3 = sS[(4 * k4 + 3) * kApplyCols + c];
+      const float s0 = sS[(4 * k4 + 0) * NC + c], s1 = sS[(4 * k4 + 1) * NC + c];
+      const float s2 = sS[(4 * k4 + 2) * NC + c], s3 = sS[(4 * k4 + 3) * NC + c];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const int i = rg * 8 + r;
+      for (int r = 0; r < kRows; ++r) {
+        const int i = rg * kRows + r;
         if (i < n) {
           const float4 qv = reinterpret_cast<const float4*>(sQg + i * d)[k4];
           o[r] += qv.x * s0 + qv.y * s1 + qv.z * s2 + qv.w * s3;
@@ -282,33 +330,35 @@ __global__ void __launch_bounds__(kApplyThreads)
         }
       }
     }
+    cp_async_wait<0>();  // B, K * exp(L_end - L) and Uv
+    __syncthreads();     // ... for every thread; everyone is done with Q * exp L and W
+    if (more) fetch_early(chunk + 1, n_next);
     if (DELTA) {
-      __syncthreads();  // nobody reads Uv from sU any more (each thread owns its entries, but rows differ below)
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const int i = rg * 8 + r;
-        if (i < n) sU[i * kApplyCols + c] -= u[r];
+      for (int r = 0; r < kRows; ++r) {
+        const int i = rg * kRows + r;
+        if (i < n) sU[i * NC + c] -= u[r];  // U = Uv - W S
       }
+      __syncthreads();  // U is whole
     }
-    __syncthreads();  // U is whole
     // ---- o_i += sum_{j <= i} B_ij u_j, rows out
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      const int i = rg * 8 + r;
+    for (int r = 0; r < kRows; ++r) {
+      const int i = rg * kRows + r;
       if (i < n) {
         float acc = o[r];
         const float* brow = sB + i * kChunk;
-        for (int j = 0; j <= i; ++j) acc += brow[j] * sU[j * kApplyCols + c];
+        for (int j = 0; j <= i; ++j) acc += brow[j] * sU[j * NC + c];
         if (col_ok) p.out[static_cast<size_t>(first + t0 + i) * (p.H * dv) + h * dv + j0 + c] = acc;
       }
     }
-    // ---- S <- diag(Eg) S + Ke^T U: this thread's rows k = rg * RPT .. + RPT - 1 of column c
+    // ---- S <- diag(exp L_end) S + (K * exp(L_end - L))^T U: rows k = rg * RPT .. + RPT - 1 of column c
     float acc[RPT];
 #pragma unroll
     for (int r = 0; r < RPT; ++r) acc[r] = 0.f;
     const int k_base = rg * RPT;
     for (int j = 0; j < n; ++j) {
-      const float uj = sU[j * kApplyCols + c];
+      const float uj = sU[j * NC + c];
       const float* krow = sKe + j * d + k_base;
 #pragma unroll
       for (int r4 = 0; r4 < RPT / 4; ++r4) {
@@ -321,16 +371,19 @@ __global__ void __launch_bounds__(kApplyThreads)
         }
       }
     }
-    __syncthreads();  // every thread has read the old S
 #pragma unroll
     for (int r = 0; r < RPT; ++r) {
       const int k = k_base + r;
-      if (k < d) sS[k * kApplyCols + c] = sEg[k] * sS[k * kApplyCols + c] + acc[r];
+      if (k < d) sS[k * NC + c] = sEg[k] * sS[k * NC + c] + acc[r];  // own entries only
     }
+    __syncthreads();  // everyone is done with B, K * exp(L_end - L), U and exp L_end
+    if (more) fetch_late(chunk + 1, n_next);
+    else cp_async_commit();  // keeps the count of groups in flight the same on the last round
   }
+  cp_async_wait<0>();
   __syncthreads();
-  for (int e = tid; e < d * kApplyCols; e += kApplyThreads) {
-    const int r = e / kApplyCols, cc = e % kApplyCols;
+  for (int e = tid; e < d * NC; e += kApplyThreads) {
+    const int r = e / NC, cc = e % NC;
     if (j0 + cc < dv) st[static_cast<size_t>(r) * dv + j0 + cc] = sS[e];
   }
 }
@@ -338,24 +391,28 @@ __global__ void __launch_bounds__(kApplyThreads)
 inline size_t prepare_smem(int d, bool delta) {
   return sizeof(float) * (static_cast<size_t>(kChunk) * (d + 1) * (delta ? 3 : 2) + (delta ? kChunk * (kChunk + 1) : 0));
 }
-inline size_t apply_smem(int d, bool delta) {
-  return sizeof(float) * (static_cast<size_t>(kChunk) * d * (delta ? 3 : 2) + kChunk * kChunk + kChunk * kApplyCols +
-                          static_cast<size_t>(d) * kApplyCols + d);
+inline size_t apply_smem(int d, bool delta, int nc = 16) {
+  return sizeof(float) * (static_cast<size_t>(kChunk) * d * (delta ? 3 : 2) + kChunk * kChunk + kChunk * nc +
+                          static_cast<size_t>(d) * nc + d);
 }
 
 template <typename S, bool DELTA>
 int launch_chunked(const ChunkArgs& a, int n_chunks, cudaStream_t stream) {
-  const size_t sp = prepare_smem(a.d, DELTA), sa = apply_smem(a.d, DELTA);
+  const size_t sp = prepare_smem(a.d, DELTA);
   auto prep = chunk_prepare_kernel<S, DELTA>;
   if (sp > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(prep, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sp));
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   launch_pdl(prep, dim3(n_chunks, a.H), dim3(kPrepThreads), sp, stream, a);
-  dim3 grid((a.dv + kApplyCols - 1) / kApplyCols, a.H, a.n_seq);
-#define PMM_APPLY_CASE(RPT)                                                                                   \
+  // 16 state columns a block; 8 where 16 would leave most of the GPU without a block
+  const bool narrow = static_cast<long long>((a.dv + 15) / 16) * a.H * a.n_seq < 100;
+  const int nc = narrow ? 8 : 16;
+  const size_t sa = apply_smem(a.d, DELTA, nc);
+  dim3 grid((a.dv + nc - 1) / nc, a.H, a.n_seq);
+#define PMM_APPLY_CASE(NC, RPT)                                                                               \
   do {                                                                                                        \
-    auto kern = chunk_apply_kernel<RPT, DELTA>;                                                               \
+    auto kern = chunk_apply_kernel<NC, RPT, DELTA>;                                                           \
     if (sa > 48 * 1024) {                                                                                     \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
                                            static_cast<int>(sa));                                             \
@@ -363,10 +420,15 @@ int launch_chunked(const ChunkArgs& a, int n_chunks, cudaStream_t stream) {
     }                                                                                                         \
     launch_pdl(kern, grid, dim3(kApplyThreads), sa, stream, a);                                               \
   } while (0)
-  if (a.d <= 32) PMM_APPLY_CASE(4);
-  else if (a.d <= 64) PMM_APPLY_CASE(8);
-  else if (a.d <= 128) PMM_APPLY_CASE(16);
-  else PMM_APPLY_CASE(32);
+  if (narrow) {
+    if (a.d <= 128) PMM_APPLY_CASE(8, 4);
+    else PMM_APPLY_CASE(8, 8);
+  } else {
+    if (a.d <= 64) PMM_APPLY_CASE(16, 4);
+    else if (a.d <= 128) PMM_APPLY_CASE(16, 8);
+    else if (a.d <= 192) PMM_APPLY_CASE(16, 12);
+    else PMM_APPLY_CASE(16, 16);
+  }
 #undef PMM_APPLY_CASE
   return launch_status();
 }

@@ -42,6 +42,8 @@ class StepContext:
     may be a LengthBounds instead, for models all of whose parts accept that).
     ``fetch_ahead``: while a layer runs, the matrices of the layer after it (set by the model;
     a layer that streams its weights once may ask the memory system for them early).
+    ``defer_output_bias``: a mixer that exposes `output_bias()` leaves the bias out while this is set (its
+    caller folds it into the launch that reads the mixer's output).
     ``unjoined_stream``: a side stream on which a layer left work running that nothing has waited
     for yet (a fetch-ahead beside its products); the model joins it before a layer that would not
     (`joins_side_stream`) and at the end of the step.
@@ -61,5 +63,6 @@ class StepContext:
     workspace: Workspace
     new_lens: List[int] = field(default_factory=list)
     past_lens: List[int] = field(default_factory=list)
+    defer_output_bias: bool = False  # set by a caller that adds a mixer's `output_bias()` itself
     fetch_ahead: Optional[List[Tensor]] = None
     unjoined_stream: Optional["torch.cuda.Stream"] = None

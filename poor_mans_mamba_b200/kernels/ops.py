@@ -63,7 +63,7 @@ _SIGNATURES = {
                             c_int, c_int, c_int, c_void_p, c_void_p],
     "pmm_hc_mix_norm": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                         c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "pmm_normed_sum": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_int, c_int, c_int, c_int,
+    "pmm_normed_sum": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_int, c_int, c_int, c_int,
                        c_void_p],
     "pmm_rope_pairs_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -1441,9 +1441,11 @@ def hc_mix_norm(lanes_in: Tensor, lanes_out: Optional[Tensor], y: Optional[Tenso
           _ptr(norm_w), float(eps), _ptr(normed), _ptr(rows), R, D, dt, y_dt, _stream())
 
 
-def normed_sum(branches: Sequence[Tuple[Tensor, Tensor]], eps: float, scale: float, out: Tensor) -> None:
-    """out = scale * sum_b rmsnorm(x_b) * w_b over up to four (x_b [T, D], w_b [D] float32); out is
-    float32 or of the branches' type."""
+def normed_sum(branches: Sequence[Tuple[Tensor, Tensor]], eps: float, scale: float, out: Tensor,
+               biases: Optional[Sequence[Optional[Tensor]]] = None) -> None:
+    """out = scale * sum_b rmsnorm(x_b + bias_b) * w_b over up to four (x_b [T, D], w_b [D] float32); out
+    is float32 or of the branches' type.  ``biases``: per branch a float32 [D] (or None) added to the
+    branch before its norm (a projection's bias that no launch of its own has to add)."""
     xs = [b[0] for b in branches]
     _cuda(out, *xs, *[b[1] for b in branches])
     T, D = out.shape
@@ -1460,8 +1462,16 @@ def normed_sum(branches: Sequence[Tuple[Tensor, Tensor]], eps: float, scale: flo
     ptrs = (ctypes.c_void_p * n)(*[x.data_ptr() for x in xs])
     lds = (ctypes.c_longlong * n)(*[x.stride(0) for x in xs])
     ws = (ctypes.c_void_p * n)(*[w.data_ptr() for _, w in branches])
+    bs = None
+    if biases is not None and any(b is not None for b in biases):
+        if len(biases) != n:
+            raise KernelError("normed_sum: one bias (or None) per branch")
+        for b in biases:
+            _cuda(b)
+            _f32vec(b, D, "normed_sum: bias")
+        bs = ctypes.cast((ctypes.c_void_p * n)(*[b.data_ptr() if b is not None else None for b in biases]), ctypes.c_void_p)
     _call("pmm_normed_sum", ctypes.cast(ptrs, ctypes.c_void_p), ctypes.cast(lds, ctypes.c_void_p),
-          ctypes.cast(ws, ctypes.c_void_p), n, float(eps), float(scale), out.data_ptr(),
+          ctypes.cast(ws, ctypes.c_void_p), bs, n, float(eps), float(scale), out.data_ptr(),
           int(out.dtype == torch.float32 and xs[0].dtype != torch.float32), T, D, _dt(xs[0]), _stream())
 
 

@@ -87,6 +87,9 @@ class NormedParallelMixer(Mixer):
             streaming.linear(x, self._fused, proj, ctx)
         main = torch.cuda.current_stream(x.device)
         side = side_streams.branch_stream(x.device, "mixer") if len(self.mixers) > 1 else None
+        # a branch's output bias is added where the branch is normed, not by a launch of its own
+        biases = [m.output_bias() for m in self.mixers]
+        ctx.defer_output_bias = True
         for i, m in enumerate(self.mixers):
             def run():
                 if proj is not None:
@@ -101,7 +104,8 @@ class NormedParallelMixer(Mixer):
                 run()
         if side is not None:
             main.wait_stream(side)
-        K.normed_sum(list(zip(outs, self.out_w)), self.eps, self.scale, out)
+        ctx.defer_output_bias = False
+        K.normed_sum(list(zip(outs, self.out_w)), self.eps, self.scale, out, biases=biases)
 
 
 register_mixer("normed_parallel", NormedParallelMixer)

@@ -131,7 +131,12 @@ class GatedDeltaMixer(_StackedInput):
         a = ws.alloc((T, self.heads * self.dim), proj.dtype)
         streaming.linear(proj[:, c0:c1], self.a2, a, ctx)
         gate = ws.alloc((T, self.v_dim), proj.dtype)
-        streaming.linear(proj[:, c1:c2], self.g2, gate, ctx)
+        # the output gate is needed only after the recurrence: its product runs beside the chain that
+        # leads there (a parallel branch of a recorded step)
+        here = torch.cuda.current_stream(proj.device)
+        side = branches.branch_stream(proj.device, "gate")
+        with branches.fork(here, side):
+            streaming.linear(proj[:, c1:c2], self.g2, gate, ctx)
         qkv = causal_conv(proj[:, :c0], self.conv_ones, None, self.conv_w, self.conv_w_t,
                           cache.fixed(f"{self.name}.conv"), ctx, activation=True)
         o = ws.alloc((T, self.v_dim), torch.float32)
@@ -147,6 +152,7 @@ class GatedDeltaMixer(_StackedInput):
             K.delta_scan(q, k, v, beta, a, self.dt_bias, self.a_log, state, ctx.cu_seqlens, ctx.slots, ctx.n_seq, o,
                          self.heads, self.kv_heads, self.dim, self.vdim, self.unit_eps, float(self.dim) ** -0.5)
         y = ws.alloc((T, self.v_dim), proj.dtype)
+        here.wait_stream(side)
         K.gated_norm(o, gate, 1.0, None, self.norm_w, self.norm_eps, self.heads, True, y, gate="sigmoid")
         streaming.linear(y, self.w_out, out, ctx)
 

@@ -105,7 +105,11 @@ class WindowSinkAttention(_StackedInput):
         attn = ws.alloc((T, self.heads * Dp), proj.dtype)
         self._attend(q_rot, kv, ctx, attn)
         streaming.linear(attn, self.w_out, out, ctx)
-        K.add_row_bias_(out, self.out_bias)
+        if not getattr(ctx, "defer_output_bias", False):
+            K.add_row_bias_(out, self.out_bias)
+
+    def output_bias(self) -> Optional[Tensor]:
+        return self.out_bias
 
 
     def _attend(self, q_rot: Tensor, kv, ctx, attn: Tensor) -> None:

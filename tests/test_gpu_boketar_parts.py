@@ -67,6 +67,10 @@ def test_normed_sum_of_branches(dtype):
     K.normed_sum([(wide[:, :D], wa.to(DEV)), (wide[:, D + 8:], wb.to(DEV))], 1e-6, 0.5, out)
     want = 0.5 * (P.norm_plain(a.double(), wa.double(), 1e-6) + P.norm_plain(b.double(), wb.double(), 1e-6))
     close(out, want, dtype, "normed sum")
+    bias = rnd(D, seed=5)  # a branch's bias joins it before its norm
+    K.normed_sum([(wide[:, :D], wa.to(DEV)), (wide[:, D + 8:], wb.to(DEV))], 1e-6, 0.5, out, biases=[None, bias.to(DEV)])
+    want = 0.5 * (P.norm_plain(a.double(), wa.double(), 1e-6) + P.norm_plain(b.double() + bias.double(), wb.double(), 1e-6))
+    close(out, want, dtype, "normed sum with a bias")
 
 
 # ----------------------------------------------------------------------------- matrix-state recurrences
