@@ -24,6 +24,7 @@
 // storage types.  Chunks start at the portion's first token; results do not depend on where a
 // portion is cut beyond rounding.
 #include "common.cuh"
+#include <utility>
 
 namespace pmm {
 
@@ -388,6 +389,131 @@ __global__ void __launch_bounds__(kApplyThreads)
   }
 }
 
+// ----------------------------------------------------------------------------------------------
+// The decayed sum has no product with the state inside its chain: S_end = a^n S_0 + N with
+// N = (K * a^(n-1-j))^T V, so the chain over a sequence's chunks is element-wise.  Three launches after
+// chunk_prepare, all but the middle one parallel over chunks: (1) N of every chunk; (2) a running
+// pass per state element that leaves every chunk's starting state where its N was; (3) the rows
+// o_i = (q_i a^(i+1))^T S_0 + sum_{j<=i} B_ij v_j of every chunk.
+constexpr int kDecayTile = 64;      // state columns per block in (1) and (3)
+constexpr int kDecayThreads = 256;
+
+// N [d, dv] per (chunk, head) -> p.W (unused by the decayed sum otherwise), chunk-major
+__global__ void __launch_bounds__(kDecayThreads)
+    decay_chunk_state_kernel(ChunkArgs p) {
+  extern __shared__ __align__(16) float sm[];
+  const int d = p.d, dv = p.dv;
+  float* sKe = sm;                    // [C][d]
+  float* sV = sKe + kChunk * d;       // [C][tile]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int chunk = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * kDecayTile;
+  int seq, t0, n;
+  if (!locate_chunk(p.cu, p.n_seq, chunk, &seq, &t0, &n)) return;
+  const int tid = threadIdx.x;
+  const size_t ch = static_cast<size_t>(chunk) * p.H + h;
+  const float* gKe = p.Ke + ch * kChunk * d;
+  const float* gV = p.Uv + ch * kChunk * dv;
+  for (int e = tid; e < n * d; e += kDecayThreads) sKe[e] = gKe[e];
+  for (int e = tid; e < n * kDecayTile; e += kDecayThreads) {
+    const int j = e / kDecayTile, c = e % kDecayTile;
+    sV[e] = (c0 + c < dv) ? gV[static_cast<size_t>(j) * dv + c0 + c] : 0.f;
+  }
+  __syncthreads();
+  float* gN = p.W + ch * static_cast<size_t>(d) * dv;
+  // thread: column c of the tile, rows k = kg, kg + 4, ...
+  const int c = tid % kDecayTile, kg = tid / kDecayTile;
+  for (int k = kg; k < d; k += kDecayThreads / kDecayTile) {
+    float acc = 0.f;
+    for (int j = 0; j < n; ++j) acc += sKe[j * d + k] * sV[j * kDecayTile + c];
+    if (c0 + c < dv) gN[static_cast<size_t>(k) * dv + c0 + c] = acc;
+  }
+}
+
+// per state element: S_0 of every chunk replaces its N; the request's state moves to the end of the portion
+__global__ void __launch_bounds__(kDecayThreads)
+    decay_chunk_scan_kernel(ChunkArgs p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seq = blockIdx.z, h = blockIdx.y;
+  const int d = p.d, dv = p.dv;
+  const int e = blockIdx.x * kDecayThreads + threadIdx.x;
+  if (e >= d * dv) return;
+  const int first = p.cu[seq], len = p.cu[seq + 1] - first;
+  if (len <= 0) return;
+  int chunk = 0;
+  for (int s = 0; s < seq; ++s) chunk += (p.cu[s + 1] - p.cu[s] + kChunk - 1) / kChunk;
+  const int k = e / dv;
+  float* st = p.state + (static_cast<size_t>(p.slots[seq]) * p.H + h) * d * dv + e;
+  float s = *st;
+  const int n_chunks = (len + kChunk - 1) / kChunk;
+  constexpr int kAhead = 8;  // the chain is one multiply-add a chunk: the loads are what takes time, so 8 fly at once
+  for (int c0 = 0; c0 < n_chunks; c0 += kAhead) {
+    float add[kAhead], eg[kAhead];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      if (c0 + u < n_chunks) {
+        const size_t ch = static_cast<size_t>(chunk + c0 + u) * p.H + h;
+        add[u] = p.W[ch * static_cast<size_t>(d) * dv + e];
+        eg[u] = p.Eg[ch * d + k];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      if (c0 + u < n_chunks) {
+        const size_t ch = static_cast<size_t>(chunk + c0 + u) * p.H + h;
+        p.W[ch * static_cast<size_t>(d) * dv + e] = s;
+        s = eg[u] * s + add[u];
+      }
+    }
+  }
+  *st = s;
+}
+
+__global__ void __launch_bounds__(kDecayThreads)
+    decay_chunk_output_kernel(ChunkArgs p) {
+  extern __shared__ __align__(16) float sm[];
+  const int d = p.d, dv = p.dv;
+  float* sQg = sm;                          // [C][d]
+  float* sB = sQg + kChunk * d;             // [C][C]
+  float* sS = sB + kChunk * kChunk;         // [d][tile]
+  float* sV = sS + d * kDecayTile;          // [C][tile]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int chunk = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * kDecayTile;
+  int seq, t0, n;
+  if (!locate_chunk(p.cu, p.n_seq, chunk, &seq, &t0, &n)) return;
+  const int tid = threadIdx.x;
+  const size_t ch = static_cast<size_t>(chunk) * p.H + h;
+  const float* gQg = p.Qg + ch * kChunk * d;
+  const float* gB = p.B + ch * kChunk * kChunk;
+  const float* gS = p.W + ch * static_cast<size_t>(d) * dv;
+  const float* gV = p.Uv + ch * kChunk * dv;
+  for (int e = tid; e < n * d; e += kDecayThreads) sQg[e] = gQg[e];
+  for (int e = tid; e < n * kChunk; e += kDecayThreads) sB[e] = gB[e];
+  for (int e = tid; e < d * kDecayTile; e += kDecayThreads) {
+    const int k = e / kDecayTile, c = e % kDecayTile;
+    sS[e] = (c0 + c < dv) ? gS[static_cast<size_t>(k) * dv + c0 + c] : 0.f;
+  }
+  for (int e = tid; e < n * kDecayTile; e += kDecayThreads) {
+    const int j = e / kDecayTile, c = e % kDecayTile;
+    sV[e] = (c0 + c < dv) ? gV[static_cast<size_t>(j) * dv + c0 + c] : 0.f;
+  }
+  __syncthreads();
+  // thread: column c, rows i = ig, ig + 4, ...: the four threads of a column take every fourth row, so
+  // the triangular sum's long and short rows are spread evenly
+  const int c = tid % kDecayTile, ig = tid / kDecayTile;
+  for (int i = ig; i < n; i += kDecayThreads / kDecayTile) {
+    float acc = 0.f;
+    const float* qrow = sQg + i * d;
+    for (int k = 0; k < d; ++k) acc += qrow[k] * sS[k * kDecayTile + c];
+    const float* brow = sB + i * kChunk;
+    for (int j = 0; j <= i; ++j) acc += brow[j] * sV[j * kDecayTile + c];
+    if (c0 + c < dv) p.out[static_cast<size_t>(t0 + i) * (p.H * dv) + h * dv + c0 + c] = acc;
+  }
+}
+
+
 inline size_t prepare_smem(int d, bool delta) {
   return sizeof(float) * (static_cast<size_t>(kChunk) * (d + 1) * (delta ? 3 : 2) + (delta ? kChunk * (kChunk + 1) : 0));
 }
@@ -405,6 +531,26 @@ int launch_chunked(const ChunkArgs& a, int n_chunks, cudaStream_t stream) {
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   launch_pdl(prep, dim3(n_chunks, a.H), dim3(kPrepThreads), sp, stream, a);
+  if (!DELTA) {
+    const int tiles = (a.dv + kDecayTile - 1) / kDecayTile;
+    const size_t s1 = sizeof(float) * kChunk * (static_cast<size_t>(a.d) + kDecayTile);
+    const size_t s3 = sizeof(float) * (static_cast<size_t>(kChunk) * a.d + kChunk * kChunk +
+                                       static_cast<size_t>(a.d) * kDecayTile + kChunk * kDecayTile);
+    if (s3 <= 200 * 1024 && tiles <= 65535) {
+      for (auto pair : {std::make_pair(decay_chunk_state_kernel, s1), std::make_pair(decay_chunk_output_kernel, s3)}) {
+        if (pair.second > 48 * 1024) {
+          cudaError_t e = cudaFuncSetAttribute(pair.first, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(pair.second));
+          if (e != cudaSuccess) return static_cast<int>(e);
+        }
+      }
+      launch_pdl(decay_chunk_state_kernel, dim3(n_chunks, a.H, tiles), dim3(kDecayThreads), s1, stream, a);
+      launch_pdl(decay_chunk_scan_kernel, dim3((a.d * a.dv + kDecayThreads - 1) / kDecayThreads, a.H, a.n_seq),
+                 dim3(kDecayThreads), 0, stream, a);
+      launch_pdl(decay_chunk_output_kernel, dim3(n_chunks, a.H, tiles), dim3(kDecayThreads), s3, stream, a);
+      return launch_status();
+    }
+  }
   // 16 state columns a block; 8 where 16 would leave most of the GPU without a block
   const bool narrow = static_cast<long long>((a.dv + 15) / 16) * a.H * a.n_seq < 100;
   const int nc = narrow ? 8 : 16;
@@ -444,7 +590,8 @@ PMM_EXPORT int pmm_recurrent_chunked_supported(int d, int delta) {
 
 // Floats of scratch per (chunk, head).
 PMM_EXPORT long long pmm_recurrent_chunked_scratch(int d, int dv, int delta) {
-  return static_cast<long long>(pmm::kChunk) * ((delta ? 3 : 2) * d + dv + pmm::kChunk) + d;
+  const long long w = delta ? static_cast<long long>(pmm::kChunk) * d : static_cast<long long>(d) * dv;  // W, or N / S_0
+  return static_cast<long long>(pmm::kChunk) * (2 * d + dv + pmm::kChunk) + w + d;
 }
 
 // n_chunks = sum over sequences of ceil(tokens / 64) (an upper bound is fine: surplus blocks leave).
@@ -469,11 +616,13 @@ PMM_EXPORT int pmm_recurrent_chunked(const void* q, long long ld_q, const void* 
   p.unit_eps = unit_eps; p.q_scale = q_scale;
   const size_t ch = static_cast<size_t>(n_chunks) * H;
   float* s = scratch;
-  // every array starts on a 16-byte boundary: their sizes are multiples of 4 floats except Eg, which is last
+  // every array starts on a 16-byte boundary where d is a multiple of 4 (the copies in 16 bytes need no
+  // more: the decayed sum's d * dv array is read with plain loads)
   p.Ke = s; s += ch * pmm::kChunk * d;
   p.Qg = s; s += ch * pmm::kChunk * d;
   p.B = s; s += ch * pmm::kChunk * pmm::kChunk;
-  if (delta) { p.W = s; s += ch * pmm::kChunk * d; }
+  p.W = s;  // delta rule: W [C, d]; decayed sum: every chunk's N, then its starting state [d, dv]
+  s += delta ? ch * pmm::kChunk * d : ch * static_cast<size_t>(d) * dv;
   p.Uv = s; s += ch * pmm::kChunk * dv;
   p.Eg = s;
   p.state = state; p.slots = slots; p.out = out;
