@@ -16,6 +16,7 @@
 //
 //   sc[s] = (q.K[s]) * scale;  p = exp(sc - max);  o = sum p V / sum p
 // (reference src/ops/gpu/attention.cu:44-105), keys lo..pos per token, lo from the window.
+#include "attention_launchers.h"
 #include "mma_helpers.cuh"
 #include <math_constants.h>
 

@@ -16,13 +16,15 @@
 //   state after the chunk of n tokens: S = diag(exp L_{n-1}) S_0 + (K * exp(L_{n-1} - L))^T U
 //
 // Only differences L_i - L_j with i >= j are ever exponentiated, so nothing overflows however strong
-// the decay.  Two launches: `chunk_prepare` makes W, Uv, B, Q * exp L, K * exp(L_end - L) and exp L_end
-// for every (chunk, head) in parallel; `chunk_apply` walks each sequence's chunks in order, a block per
-// (sequence, head, 16 state columns), with three small matrix products per chunk and the next chunk's
-// operands fetched meanwhile.  All arithmetic is
-// float on the CUDA cores: scores, decays, the triangular solve and the state stay 32-bit in both
-// storage types.  Chunks start at the portion's first token; results do not depend on where a
-// portion is cut beyond rounding.
+// the decay.  `chunk_prepare` makes W, Uv, B, Q * exp L, K * exp(L_end - L) and exp L_end for every
+// (chunk, head) in parallel.  What follows keeps the chain from chunk to chunk as short as it can be
+// and does everything else in parallel over chunks (see the two groups of kernels below): for the
+// decayed sum the chain is element-wise, for the delta rule it is one product S <- M S + N per chunk.
+// `chunk_apply` is the first, direct form (three products with the state per chunk inside the chain);
+// it stays for sizes whose operands the later kernels cannot hold.  All arithmetic is float on the
+// CUDA cores: scores, decays, the triangular solve and the state stay 32-bit in both storage types.
+// Chunks start at the portion's first token; results do not depend on where a portion is cut beyond
+// rounding.
 #include "common.cuh"
 #include <utility>
 
@@ -46,6 +48,7 @@ struct ChunkArgs {
   float unit_eps, q_scale;
   // per (chunk, head), chunk-major: W [C, d] (delta), Uv [C, dv], B [C, C], Qg [C, d], Ke [C, d], Eg [d]
   float *W, *Uv, *B, *Qg, *Ke, *Eg;
+  float *N, *M;                         // [d, dv] and (delta) [d, d] per (chunk, head): see the kernels that use them
   float* state; const int* slots; float* out;
 };
 
@@ -398,7 +401,53 @@ __global__ void __launch_bounds__(kApplyThreads)
 constexpr int kDecayTile = 64;      // state columns per block in (1) and (3)
 constexpr int kDecayThreads = 256;
 
-// N [d, dv] per (chunk, head) -> p.W (unused by the decayed sum otherwise), chunk-major
+// ---- small products on shared-memory operands, 4 x 4 results a thread (16 multiply-adds per two
+// 16-byte loads).  Tiles are 64 columns wide; thread t of 256 owns columns 4 (t % 16) .. + 3.
+__device__ __forceinline__ void fma4x4(float (&acc)[4][4], const float4& a, const float4& b) {
+  const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[r][c] += av[r] * bv[c];
+}
+
+// acc[r][c] = sum_{j < n} A[j][k0 + r] * R[j][c0 + c]   (A rows of stride lda, R rows of stride 64)
+__device__ __forceinline__ void product_tn(float (&acc)[4][4], const float* __restrict__ A, int lda, int k0,
+                                           const float* __restrict__ R, int c0, int n) {
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+  for (int j = 0; j < n; ++j)
+    fma4x4(acc, *reinterpret_cast<const float4*>(A + j * lda + k0), *reinterpret_cast<const float4*>(R + j * kDecayTile + c0));
+}
+
+// acc[r][c] += sum_{k < kn} A[i0 + r][k] * R[k][c0 + c], kn a multiple of 4; with `tri`, only k <= i0 + r
+__device__ __forceinline__ void product_nn(float (&acc)[4][4], const float* __restrict__ A, int lda, int i0,
+                                           const float* __restrict__ R, int c0, int kn, bool tri) {
+  for (int k4 = 0; k4 < kn; k4 += 4) {
+    float4 a[4], b[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const float4*>(A + (i0 + r) * lda + k4);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) b[q] = *reinterpret_cast<const float4*>(R + (k4 + q) * kDecayTile + c0);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const float av[4] = {a[r].x, a[r].y, a[r].z, a[r].w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (!tri || k4 + q <= i0 + r) {
+          acc[r][0] += av[q] * b[q].x;
+          acc[r][1] += av[q] * b[q].y;
+          acc[r][2] += av[q] * b[q].z;
+          acc[r][3] += av[q] * b[q].w;
+        }
+      }
+    }
+  }
+}
+
+// N [d, dv] per (chunk, head), chunk-major
 __global__ void __launch_bounds__(kDecayThreads)
     decay_chunk_state_kernel(ChunkArgs p) {
   extern __shared__ __align__(16) float sm[];
@@ -420,13 +469,16 @@ __global__ void __launch_bounds__(kDecayThreads)
     sV[e] = (c0 + c < dv) ? gV[static_cast<size_t>(j) * dv + c0 + c] : 0.f;
   }
   __syncthreads();
-  float* gN = p.W + ch * static_cast<size_t>(d) * dv;
-  // thread: column c of the tile, rows k = kg, kg + 4, ...
-  const int c = tid % kDecayTile, kg = tid / kDecayTile;
-  for (int k = kg; k < d; k += kDecayThreads / kDecayTile) {
-    float acc = 0.f;
-    for (int j = 0; j < n; ++j) acc += sKe[j * d + k] * sV[j * kDecayTile + c];
-    if (c0 + c < dv) gN[static_cast<size_t>(k) * dv + c0 + c] = acc;
+  float* gN = p.N + ch * static_cast<size_t>(d) * dv;
+  const int cc = 4 * (tid % 16);
+  for (int k0 = 4 * (tid / 16); k0 < d; k0 += 4 * (kDecayThreads / 16)) {
+    float acc[4][4];
+    product_tn(acc, sKe, d, k0, sV, cc, n);
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (c0 + cc + c < dv) gN[static_cast<size_t>(k0 + r) * dv + c0 + cc + c] = acc[r][c];
   }
 }
 
@@ -454,7 +506,7 @@ __global__ void __launch_bounds__(kDecayThreads)
     for (int u = 0; u < kAhead; ++u) {
       if (c0 + u < n_chunks) {
         const size_t ch = static_cast<size_t>(chunk + c0 + u) * p.H + h;
-        add[u] = p.W[ch * static_cast<size_t>(d) * dv + e];
+        add[u] = p.N[ch * static_cast<size_t>(d) * dv + e];
         eg[u] = p.Eg[ch * d + k];
       }
     }
@@ -462,7 +514,7 @@ __global__ void __launch_bounds__(kDecayThreads)
     for (int u = 0; u < kAhead; ++u) {
       if (c0 + u < n_chunks) {
         const size_t ch = static_cast<size_t>(chunk + c0 + u) * p.H + h;
-        p.W[ch * static_cast<size_t>(d) * dv + e] = s;
+        p.N[ch * static_cast<size_t>(d) * dv + e] = s;
         s = eg[u] * s + add[u];
       }
     }
@@ -487,7 +539,7 @@ __global__ void __launch_bounds__(kDecayThreads)
   const size_t ch = static_cast<size_t>(chunk) * p.H + h;
   const float* gQg = p.Qg + ch * kChunk * d;
   const float* gB = p.B + ch * kChunk * kChunk;
-  const float* gS = p.W + ch * static_cast<size_t>(d) * dv;
+  const float* gS = p.N + ch * static_cast<size_t>(d) * dv;
   const float* gV = p.Uv + ch * kChunk * dv;
   for (int e = tid; e < n * d; e += kDecayThreads) sQg[e] = gQg[e];
   for (int e = tid; e < n * kChunk; e += kDecayThreads) sB[e] = gB[e];
@@ -500,19 +552,219 @@ __global__ void __launch_bounds__(kDecayThreads)
     sV[e] = (c0 + c < dv) ? gV[static_cast<size_t>(j) * dv + c0 + c] : 0.f;
   }
   __syncthreads();
-  // thread: column c, rows i = ig, ig + 4, ...: the four threads of a column take every fourth row, so
-  // the triangular sum's long and short rows are spread evenly
-  const int c = tid % kDecayTile, ig = tid / kDecayTile;
-  for (int i = ig; i < n; i += kDecayThreads / kDecayTile) {
-    float acc = 0.f;
-    const float* qrow = sQg + i * d;
-    for (int k = 0; k < d; ++k) acc += qrow[k] * sS[k * kDecayTile + c];
-    const float* brow = sB + i * kChunk;
-    for (int j = 0; j <= i; ++j) acc += brow[j] * sV[j * kDecayTile + c];
-    if (c0 + c < dv) p.out[static_cast<size_t>(t0 + i) * (p.H * dv) + h * dv + c0 + c] = acc;
+  // thread: rows i0 .. i0 + 3, columns cc .. cc + 3 (rows at and beyond n hold stale values that are not stored)
+  const int cc = 4 * (tid % 16), i0 = 4 * (tid / 16);
+  if (i0 < n) {
+    float acc[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+    product_nn(acc, sQg, d, i0, sS, cc, d, false);
+    product_nn(acc, sB, kChunk, i0, sV, cc, i0 + 4, true);
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (i0 + r < n && c0 + cc + c < dv)
+          p.out[static_cast<size_t>(t0 + i0 + r) * (p.H * dv) + h * dv + c0 + cc + c] = acc[r][c];
   }
 }
 
+// ----------------------------------------------------------------------------------------------
+// The delta rule's link from chunk to chunk, S_end = diag(exp L_end) S_0 + Ke^T (Uv - W S_0) with
+// Ke = K * exp(L_end - L), is one product with the state once it is written as
+//   S_end = M S_0 + N,    M = diag(exp L_end) - Ke^T W  [d, d],    N = Ke^T Uv  [d, dv],
+// and M and N do not depend on the state.  Three launches after chunk_prepare: (1) M and N of every
+// chunk in parallel; (2) the chain, a block per (sequence, head, 8 state columns), one product a chunk,
+// the next chunk's M fetched meanwhile, every chunk's starting state left where its N was; (3) the
+// rows o_i = (q_i * exp L_i)^T S_0 + sum_{j<=i} B_ij u_j, U = Uv - W S_0, of every chunk in parallel.
+constexpr int kChainCols = 8;
+
+// X = Ke^T [-W | Uv]: columns below d go to M (with exp L_end on the diagonal), the others to N
+__global__ void __launch_bounds__(kDecayThreads)
+    delta_chunk_compose_kernel(ChunkArgs p, float* __restrict__ gM_all) {
+  extern __shared__ __align__(16) float sm[];
+  const int d = p.d, dv = p.dv;
+  float* sKe = sm;                    // [C][d]
+  float* sR = sKe + kChunk * d;       // [C][tile]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int chunk = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * kDecayTile;
+  int seq, t0, n;
+  if (!locate_chunk(p.cu, p.n_seq, chunk, &seq, &t0, &n)) return;
+  const int tid = threadIdx.x;
+  const size_t ch = static_cast<size_t>(chunk) * p.H + h;
+  const float* gKe = p.Ke + ch * kChunk * d;
+  const float* gW = p.W + ch * kChunk * d;
+  const float* gUv = p.Uv + ch * kChunk * dv;
+  for (int e = tid; e < n * d; e += kDecayThreads) sKe[e] = gKe[e];
+  for (int e = tid; e < n * kDecayTile; e += kDecayThreads) {
+    const int j = e / kDecayTile, col = c0 + e % kDecayTile;
+    float v = 0.f;
+    if (col < d) v = -gW[static_cast<size_t>(j) * d + col];
+    else if (col < d + dv) v = gUv[static_cast<size_t>(j) * dv + col - d];
+    sR[e] = v;
+  }
+  __syncthreads();
+  float* gM = gM_all + ch * static_cast<size_t>(d) * d;
+  float* gN = p.N + ch * static_cast<size_t>(d) * dv;
+  const int cc = 4 * (tid % 16);
+  for (int k0 = 4 * (tid / 16); k0 < d; k0 += 4 * (kDecayThreads / 16)) {
+    float acc[4][4];
+    product_tn(acc, sKe, d, k0, sR, cc, n);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int k = k0 + r, col = c0 + cc + c;
+        if (col < d) gM[static_cast<size_t>(k) * d + col] = acc[r][c] + (k == col ? p.Eg[ch * d + k] : 0.f);
+        else if (col < d + dv) gN[static_cast<size_t>(k) * dv + col - d] = acc[r][c];
+      }
+    }
+  }
+}
+
+template <int RPT>  // rows of S per thread: d <= 32 * RPT
+__global__ void __launch_bounds__(kDecayThreads)
+    delta_chunk_chain_kernel(ChunkArgs p, const float* __restrict__ gM_all, int n_buf) {
+  extern __shared__ __align__(16) float sm[];
+  const int d = p.d, dv = p.dv;
+  float* sM = sm;                                   // [n_buf][d][d]
+  float* sS = sM + static_cast<size_t>(n_buf) * d * d;  // [d][NC]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seq = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * kChainCols;
+  const int tid = threadIdx.x;
+  const int c = tid % kChainCols, kg = tid / kChainCols;  // 32 row groups
+  const int first = p.cu[seq], len = p.cu[seq + 1] - first;
+  if (len <= 0) return;
+  int chunk0 = 0;
+  for (int s = 0; s < seq; ++s) chunk0 += (p.cu[s + 1] - p.cu[s] + kChunk - 1) / kChunk;
+  const int n_chunks = (len + kChunk - 1) / kChunk;
+  const bool col_ok = j0 + c < dv;
+  const int dd4 = d * d / 4, d4 = d / 4;
+  float* st = p.state + ((static_cast<size_t>(p.slots[seq]) * p.H + h) * d) * dv;
+  auto fetch = [&](int ci) {
+    const float* gM = gM_all + (static_cast<size_t>(chunk0 + ci) * p.H + h) * static_cast<size_t>(d) * d;
+    float* dst = sM + static_cast<size_t>(ci % n_buf) * d * d;
+    for (int e = tid; e < dd4; e += kDecayThreads) cp_async16(dst + 4 * e, gM + 4 * e);
+    cp_async_commit();
+  };
+  fetch(0);
+  for (int e = tid; e < d * kChainCols; e += kDecayThreads) {
+    const int r = e / kChainCols, cc = e % kChainCols;
+    sS[e] = (j0 + cc < dv) ? st[static_cast<size_t>(r) * dv + j0 + cc] : 0.f;
+  }
+  for (int ci = 0; ci < n_chunks; ++ci) {
+    if (n_buf > 1 && ci + 1 < n_chunks) {
+      fetch(ci + 1);        // into the other buffer, whose product ended before the barrier below
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();        // M of this chunk and everyone's rows of S are there
+    const float* M = sM + static_cast<size_t>(ci % n_buf) * d * d;
+    float* gN = p.N + (static_cast<size_t>(chunk0 + ci) * p.H + h) * static_cast<size_t>(d) * dv;
+    float acc[RPT], nv[RPT];
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {  // N comes from global memory while the product runs
+      const int k = kg + 32 * r;
+      nv[r] = (k < d && col_ok) ? gN[static_cast<size_t>(k) * dv + j0 + c] : 0.f;
+      acc[r] = 0.f;
+    }
+    for (int q4 = 0; q4 < d4; ++q4) {
+      const float s0 = sS[(4 * q4 + 0) * kChainCols + c], s1 = sS[(4 * q4 + 1) * kChainCols + c];
+      const float s2 = sS[(4 * q4 + 2) * kChainCols + c], s3 = sS[(4 * q4 + 3) * kChainCols + c];
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        const int k = kg + 32 * r;
+        if (k < d) {
+          const float4 m = reinterpret_cast<const float4*>(M + static_cast<size_t>(k) * d)[q4];
+          acc[r] += m.x * s0 + m.y * s1 + m.z * s2 + m.w * s3;
+        }
+      }
+    }
+    __syncthreads();        // everyone has read S (and this chunk's M)
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+      const int k = kg + 32 * r;
+      if (k < d) {
+        if (col_ok) gN[static_cast<size_t>(k) * dv + j0 + c] = sS[k * kChainCols + c];  // the chunk's starting state
+        sS[k * kChainCols + c] = acc[r] + nv[r];
+      }
+    }
+    if (n_buf == 1 && ci + 1 < n_chunks) fetch(ci + 1);
+  }
+  __syncthreads();
+  for (int e = tid; e < d * kChainCols; e += kDecayThreads) {
+    const int r = e / kChainCols, cc = e % kChainCols;
+    if (j0 + cc < dv) st[static_cast<size_t>(r) * dv + j0 + cc] = sS[e];
+  }
+}
+
+__global__ void __launch_bounds__(kDecayThreads)
+    delta_chunk_output_kernel(ChunkArgs p) {
+  extern __shared__ __align__(16) float sm[];
+  const int d = p.d, dv = p.dv;
+  float* sQg = sm;                          // [C][d]
+  float* sW = sQg + kChunk * d;             // [C][d]
+  float* sB = sW + kChunk * d;              // [C][C]
+  float* sS = sB + kChunk * kChunk;         // [d][tile]
+  float* sU = sS + d * kDecayTile;          // [C][tile]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int chunk = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * kDecayTile;
+  int seq, t0, n;
+  if (!locate_chunk(p.cu, p.n_seq, chunk, &seq, &t0, &n)) return;
+  const int tid = threadIdx.x;
+  const size_t ch = static_cast<size_t>(chunk) * p.H + h;
+  const float* gQg = p.Qg + ch * kChunk * d;
+  const float* gW = p.W + ch * kChunk * d;
+  const float* gB = p.B + ch * kChunk * kChunk;
+  const float* gS = p.N + ch * static_cast<size_t>(d) * dv;
+  const float* gUv = p.Uv + ch * kChunk * dv;
+  const int d4 = d / 4;
+  for (int e = tid; e < n * d4; e += kDecayThreads) {
+    reinterpret_cast<float4*>(sQg)[e] = reinterpret_cast<const float4*>(gQg)[e];
+    reinterpret_cast<float4*>(sW)[e] = reinterpret_cast<const float4*>(gW)[e];
+  }
+  for (int e = tid; e < n * kChunk; e += kDecayThreads) sB[e] = gB[e];
+  for (int e = tid; e < d * kDecayTile; e += kDecayThreads) {
+    const int k = e / kDecayTile, c = e % kDecayTile;
+    sS[e] = (c0 + c < dv) ? gS[static_cast<size_t>(k) * dv + c0 + c] : 0.f;
+  }
+  for (int e = tid; e < n * kDecayTile; e += kDecayThreads) {
+    const int j = e / kDecayTile, c = e % kDecayTile;
+    sU[e] = (c0 + c < dv) ? gUv[static_cast<size_t>(j) * dv + c0 + c] : 0.f;
+  }
+  __syncthreads();
+  // thread: rows i0 .. i0 + 3, columns cc .. cc + 3
+  const int cc = 4 * (tid % 16), i0 = 4 * (tid / 16);
+  float o[4][4], u[4][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[r][c] = u[r][c] = 0.f;
+  if (i0 < n) {
+    product_nn(o, sQg, d, i0, sS, cc, d, false);
+    product_nn(u, sW, d, i0, sS, cc, d, false);
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) sU[(i0 + r) * kDecayTile + cc + c] -= u[r][c];  // U = Uv - W S_0 (own entries)
+  }
+  __syncthreads();
+  if (i0 < n) {
+    product_nn(o, sB, kChunk, i0, sU, cc, i0 + 4, true);
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (i0 + r < n && c0 + cc + c < dv)
+          p.out[static_cast<size_t>(t0 + i0 + r) * (p.H * dv) + h * dv + c0 + cc + c] = o[r][c];
+  }
+}
 
 inline size_t prepare_smem(int d, bool delta) {
   return sizeof(float) * (static_cast<size_t>(kChunk) * (d + 1) * (delta ? 3 : 2) + (delta ? kChunk * (kChunk + 1) : 0));
@@ -531,6 +783,29 @@ int launch_chunked(const ChunkArgs& a, int n_chunks, cudaStream_t stream) {
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   launch_pdl(prep, dim3(n_chunks, a.H), dim3(kPrepThreads), sp, stream, a);
+  if (DELTA) {
+    const int d = a.d;
+    const int tiles_c = (d + a.dv + kDecayTile - 1) / kDecayTile, tiles_o = (a.dv + kDecayTile - 1) / kDecayTile;
+    const size_t s1 = sizeof(float) * kChunk * (static_cast<size_t>(d) + kDecayTile);
+    const size_t m_bytes = sizeof(float) * static_cast<size_t>(d) * d, s_bytes = sizeof(float) * d * kChainCols;
+    const int n_buf = 2 * m_bytes + s_bytes <= 200 * 1024 ? 2 : 1;
+    const size_t s2 = n_buf * m_bytes + s_bytes;
+    const size_t s3 = sizeof(float) * (2 * static_cast<size_t>(kChunk) * d + kChunk * kChunk +
+                                       static_cast<size_t>(d) * kDecayTile + kChunk * kDecayTile);
+    if (s2 <= 200 * 1024 && s3 <= 200 * 1024) {
+      auto chain = d <= 64 ? delta_chunk_chain_kernel<2> : d <= 128 ? delta_chunk_chain_kernel<4> : delta_chunk_chain_kernel<8>;
+      cudaError_t e = cudaSuccess;
+      if (s1 > 48 * 1024) e = cudaFuncSetAttribute(delta_chunk_compose_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(s1));
+      if (e == cudaSuccess && s2 > 48 * 1024) e = cudaFuncSetAttribute(chain, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(s2));
+      if (e == cudaSuccess && s3 > 48 * 1024) e = cudaFuncSetAttribute(delta_chunk_output_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(s3));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      launch_pdl(delta_chunk_compose_kernel, dim3(n_chunks, a.H, tiles_c), dim3(kDecayThreads), s1, stream, a, a.M);
+      launch_pdl(chain, dim3((a.dv + kChainCols - 1) / kChainCols, a.H, a.n_seq), dim3(kDecayThreads), s2, stream, a,
+                 static_cast<const float*>(a.M), n_buf);
+      launch_pdl(delta_chunk_output_kernel, dim3(n_chunks, a.H, tiles_o), dim3(kDecayThreads), s3, stream, a);
+      return launch_status();
+    }
+  }
   if (!DELTA) {
     const int tiles = (a.dv + kDecayTile - 1) / kDecayTile;
     const size_t s1 = sizeof(float) * kChunk * (static_cast<size_t>(a.d) + kDecayTile);
@@ -590,8 +865,9 @@ PMM_EXPORT int pmm_recurrent_chunked_supported(int d, int delta) {
 
 // Floats of scratch per (chunk, head).
 PMM_EXPORT long long pmm_recurrent_chunked_scratch(int d, int dv, int delta) {
-  const long long w = delta ? static_cast<long long>(pmm::kChunk) * d : static_cast<long long>(d) * dv;  // W, or N / S_0
-  return static_cast<long long>(pmm::kChunk) * (2 * d + dv + pmm::kChunk) + w + d;
+  // Ke, Qg, Uv, B, Eg; N (then every chunk's starting state); for the delta rule also W and M
+  const long long w = delta ? static_cast<long long>(pmm::kChunk) * d + static_cast<long long>(d) * d : 0;
+  return static_cast<long long>(pmm::kChunk) * (2 * d + dv + pmm::kChunk) + static_cast<long long>(d) * dv + w + d;
 }
 
 // n_chunks = sum over sequences of ceil(tokens / 64) (an upper bound is fine: surplus blocks leave).
@@ -621,8 +897,11 @@ PMM_EXPORT int pmm_recurrent_chunked(const void* q, long long ld_q, const void* 
   p.Ke = s; s += ch * pmm::kChunk * d;
   p.Qg = s; s += ch * pmm::kChunk * d;
   p.B = s; s += ch * pmm::kChunk * pmm::kChunk;
-  p.W = s;  // delta rule: W [C, d]; decayed sum: every chunk's N, then its starting state [d, dv]
-  s += delta ? ch * pmm::kChunk * d : ch * static_cast<size_t>(d) * dv;
+  p.N = s; s += ch * static_cast<size_t>(d) * dv;
+  if (delta) {
+    p.W = s; s += ch * pmm::kChunk * d;
+    p.M = s; s += ch * static_cast<size_t>(d) * d;
+  }
   p.Uv = s; s += ch * pmm::kChunk * dv;
   p.Eg = s;
   p.state = state; p.slots = slots; p.out = out;

@@ -95,7 +95,10 @@ def add_products(h: Tensor, products: Sequence[Tuple[Tensor, Tensor, float]], ct
 
 def _streams(x: Tensor, w: Tensor, out: Tensor, ctx) -> bool:
     """Whether a product of these operands may take the weight-streaming kernels."""
-    return (eligible(ctx, x.shape[1]) and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    if not (x.dim() == 2 and x.dtype == torch.bfloat16 and x.shape[0] <= K.SKINNY_MAX_TOKENS and x.shape[1] % 8 == 0
+            and K.skinny_fits(x.shape[0], x.shape[1])):
+        return False  # (decided by the operands alone: callers may hand over a context that holds only a workspace)
+    return (x.stride(1) == 1
             and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous() and w.data_ptr() % 16 == 0
             and out.stride(1) == 1 and out.dtype == torch.bfloat16)
 

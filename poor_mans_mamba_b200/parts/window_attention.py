@@ -119,7 +119,8 @@ class WindowSinkAttention(_StackedInput):
         mma.sync); float32, and any other head size, on the float kernel."""
         T, H, G, Dp, ws = q_rot.shape[0], self.heads, self.kv_heads, self.padded_dim, ctx.workspace
         counter = self._split_counter
-        bf16 = q_rot.dtype == torch.bfloat16 and counter is not None
+        # (the tensor-core kernels take the row maximum before the scale is applied: positive scales only)
+        bf16 = q_rot.dtype == torch.bfloat16 and counter is not None and self.scale > 0.0
 
         def scratch_for(n_splits):
             return ws.alloc((K.attention_scratch_floats(T, H, Dp, n_splits),), torch.float32) if n_splits > 1 else None

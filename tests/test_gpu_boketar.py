@@ -177,3 +177,20 @@ def test_trace_program_replays_a_schedule(case, tmp_path):
     want2 = torch.stack([refs[3][-1], refs[1][1]])
     H.check_rows(torch.from_numpy(s0), want0, "float32", "trace step 0", f32_frac=F32_FRAC)
     H.check_rows(torch.from_numpy(s2), want2, "float32", "trace step 2", f32_frac=F32_FRAC)
+
+
+def test_command_line_generates_from_a_model_folder(case):
+    which, d, cfg, weights, seqs, refs = case
+    if which != "B":
+        pytest.skip("one configuration is enough for the program")
+    prompt = ",".join(str(t) for t in seqs[2])
+    proc = subprocess.run([sys.executable, "-m", "poor_mans_mamba_b200", d, "64", "GPU", "1", "2", "5", "--dtype", "float32",
+                           "--prompt-ids", prompt, "--page-size", "16"], capture_output=True, text=True, timeout=600,
+                          cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [l for l in proc.stdout.splitlines() if l.startswith("req_id=")]
+    assert len(lines) == 2 and all("gen_tokens=5" in l for l in lines)
+    toks = list(seqs[2])
+    for _ in range(5):
+        toks.append(int(P.forward(cfg, weights, toks, torch.float64)[-1].argmax()))
+    assert str(toks[len(seqs[2]):]) in lines[0]
