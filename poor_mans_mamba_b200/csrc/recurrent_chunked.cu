@@ -48,6 +48,7 @@ struct ChunkArgs {
   float unit_eps, q_scale;
   // per (chunk, head), chunk-major: W [C, d] (delta), Uv [C, dv], B [C, C], Qg [C, d], Ke [C, d], Eg [d]
   float *W, *Uv, *B, *Qg, *Ke, *Eg;
+  int sub_blocks;                       // chunk_prepare scales rows once per sub-block of 16 tokens (its shared memory allows it)
   float *N, *M;                         // [d, dv] and (delta) [d, d] per (chunk, head): see the kernels that use them
   float* state; const int* slots; float* out;
 };
@@ -142,7 +143,64 @@ __global__ void __launch_bounds__(kPrepThreads)
     __syncthreads();
   }
 
-  // ---- A (delta) and B: a warp takes rows i, a lane the columns j = lane and lane + 32
+  // ---- A (delta) and B
+  if (DELTA && p.sub_blocks) {
+    // Pairs inside one sub-block of 16 tokens: the exponential per channel.  A warp takes two rows,
+    // 16 lanes each, a lane one column of the row's sub-block.
+    for (int i2 = 2 * warp; i2 < n; i2 += 2 * (kPrepThreads / 32)) {
+      const int i = i2 + (lane >> 4), j = (i & ~15) + (lane & 15);
+      if (i < n && j <= i) {
+        const float *qi = sQ + i * ds, *ki = sK + i * ds, *li = sL + i * ds, *kj = sK + j * ds, *lj = sL + j * ds;
+        float accA = 0.f, accB = 0.f;
+        for (int c = 0; c < d; ++c) {
+          const float w = expf(li[c] - lj[c]) * kj[c];
+          accA += ki[c] * w;
+          accB += qi[c] * w;
+        }
+        sA[i * (kChunk + 1) + j] = accA;
+        oB[i * kChunk + j] = accB;
+      }
+    }
+    // Pairs across sub-blocks: with r the last row before i's sub-block, exp(L_i - L_j) = exp(L_i - L_r) exp(L_r - L_j),
+    // both factors at most one, so the rows are scaled once per sub-block and the pairs are plain dot products.
+    float* sKd = sA + kChunk * (kChunk + 1);   // [48][ds]  k_j exp(L_r - L_j), j before the sub-block
+    float* sKp = sKd + 48 * ds;                // [16][ds]  k_i exp(L_i - L_r), i in the sub-block
+    float* sQp = sKp + 16 * ds;                // [16][ds]  q_i exp(L_i - L_r)
+    for (int blk = 1; 16 * blk < n; ++blk) {
+      const int r = 16 * blk - 1, rows = min(16, n - 16 * blk);
+      __syncthreads();  // the sub-block before is done with the scaled rows
+      for (int e = tid; e < 16 * blk * d; e += kPrepThreads) {
+        const int j = e / d, c = e - j * d;
+        sKd[j * ds + c] = sK[j * ds + c] * expf(sL[r * ds + c] - sL[j * ds + c]);
+      }
+      for (int e = tid; e < rows * d; e += kPrepThreads) {
+        const int ii = e / d, c = e - ii * d, i = 16 * blk + ii;
+        const float pw = expf(sL[i * ds + c] - sL[r * ds + c]);
+        sKp[ii * ds + c] = sK[i * ds + c] * pw;
+        sQp[ii * ds + c] = sQ[i * ds + c] * pw;
+      }
+      __syncthreads();
+      if (warp < rows) {  // a warp per row of the sub-block, a lane the columns j = lane and lane + 32
+        const int i = 16 * blk + warp;
+        const float *kp = sKp + warp * ds, *qp = sQp + warp * ds;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int j = lane + 32 * half;
+          if (j < 16 * blk) {
+            const float* kd = sKd + j * ds;
+            float accA = 0.f, accB = 0.f;
+            for (int c = 0; c < d; ++c) {
+              accA += kp[c] * kd[c];
+              accB += qp[c] * kd[c];
+            }
+            sA[i * (kChunk + 1) + j] = accA;
+            oB[i * kChunk + j] = accB;
+          }
+        }
+      }
+    }
+  } else {
+  // a warp takes rows i, a lane the columns j = lane and lane + 32
   for (int i = warp; i < n; i += kPrepThreads / 32) {
     const float* qi = sQ + i * ds;
     const float* ki = sK + i * ds;
@@ -167,6 +225,7 @@ __global__ void __launch_bounds__(kPrepThreads)
       }
       oB[i * kChunk + j] = accB;
     }
+  }
   }
   // ---- q * exp L, k * exp(L_end - L), exp L_end
   for (int e = tid; e < n * d; e += kPrepThreads) {
@@ -766,8 +825,9 @@ __global__ void __launch_bounds__(kDecayThreads)
   }
 }
 
-inline size_t prepare_smem(int d, bool delta) {
-  return sizeof(float) * (static_cast<size_t>(kChunk) * (d + 1) * (delta ? 3 : 2) + (delta ? kChunk * (kChunk + 1) : 0));
+inline size_t prepare_smem(int d, bool delta, bool sub_blocks = false) {
+  return sizeof(float) * (static_cast<size_t>(kChunk) * (d + 1) * (delta ? 3 : 2) + (delta ? kChunk * (kChunk + 1) : 0) +
+                          (sub_blocks ? static_cast<size_t>(48 + 32) * (d + 1) : 0));
 }
 inline size_t apply_smem(int d, bool delta, int nc = 16) {
   return sizeof(float) * (static_cast<size_t>(kChunk) * d * (delta ? 3 : 2) + kChunk * kChunk + kChunk * nc +
@@ -775,8 +835,9 @@ inline size_t apply_smem(int d, bool delta, int nc = 16) {
 }
 
 template <typename S, bool DELTA>
-int launch_chunked(const ChunkArgs& a, int n_chunks, cudaStream_t stream) {
-  const size_t sp = prepare_smem(a.d, DELTA);
+int launch_chunked(ChunkArgs a, int n_chunks, cudaStream_t stream) {
+  a.sub_blocks = DELTA && prepare_smem(a.d, true, true) <= 220 * 1024;
+  const size_t sp = prepare_smem(a.d, DELTA, a.sub_blocks != 0);
   auto prep = chunk_prepare_kernel<S, DELTA>;
   if (sp > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(prep, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sp));
