@@ -66,7 +66,28 @@ BK_C = {
     ],
 }
 
-CONFIGS = {"A": BK_A, "B": BK_B, "C": BK_C}
+# Sizes at which the tensor-core and vector forms of the kernels are the ones that run: head sizes of 64 and
+# 128 (with a value size that is padded), key sizes the chunked recurrences take, rows of whole 16-byte groups.
+BK_M = {
+    "architecture": "Boketar", "vocab": 1000, "width": 384, "streams": 4,
+    "embedding": {"scale": 2.0}, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "parallel", "mlp": {"kind": "dense", "ff": 512}, "mixer": {
+            "left": {"heads": 4, "kv_heads": 2, "dim": 128, "vdim": 96, "conv": 3, "mask": {"size": 300},
+                     "rot": {"dims": 64, "base": 100000.0}, "scale": 0.1},
+            "right": {"heads": 4, "dim": 64, "vdim": 64, "decay": [0.9, 0.99, 0.999, 0.9999]}}},
+        {"type": "channel_delta", "mlp": {"kind": "dense", "ff": 768}, "mixer": {
+            "heads": 4, "kv_heads": 2, "dim": 128, "vdim": 64, "conv": 4, "decay_rank": 32, "gate_rank": 16}},
+        {"type": "parallel", "mlp": None, "mixer": {
+            "left": {"heads": 8, "kv_heads": 1, "dim": 64, "vdim": 64, "conv": 2, "mask": {"size": 64},
+                     "rot": {"dims": 64, "base": 10000.0}, "scale": 0.125},
+            "right": {"heads": 2, "dim": 128, "vdim": 128, "decay": [0.97, 1.0]}}},
+        {"type": "channel_delta", "mlp": None, "mixer": {
+            "heads": 6, "kv_heads": 6, "dim": 64, "vdim": 128, "conv": 2, "decay_rank": 8, "gate_rank": 8}},
+    ],
+}
+
+CONFIGS = {"A": BK_A, "B": BK_B, "C": BK_C, "M": BK_M}
 
 
 def config(which: str) -> dict:

@@ -194,3 +194,21 @@ def test_command_line_generates_from_a_model_folder(case):
     for _ in range(5):
         toks.append(int(P.forward(cfg, weights, toks, torch.float64)[-1].argmax()))
     assert str(toks[len(seqs[2]):]) in lines[0]
+
+
+def test_medium_sizes_where_the_tensor_core_forms_run(tmp_path):
+    """Head sizes of 64 and 128, a padded value size, prompts long enough for the tcgen05 attention and the
+    chunked recurrences, pages of 64 tokens: whole, in portions that cut chunks and windows anywhere, and
+    with a long tail decoded through the TMA decode attention."""
+    d, cfg, weights = B.make_model_dir("M", str(tmp_path), seed=21)
+    seqs = B.sequences(cfg, (700, 333), seed=9)
+    refs = refs_of(cfg, weights, seqs)
+    for dtype in ("float32", "bfloat16"):
+        for name, script in (("whole", H.script_whole(seqs)),
+                             ("tail", H.script_tail_one_by_one(seqs, tail=80)),
+                             ("portions", [([(0, 0, 257)], []), ([(0, 257, 2), (1, 0, 130)], []),
+                                           ([(0, 259, 300), (1, 130, 1)], []), ([(0, 559, 141), (1, 131, 202)], [0, 1])])):
+            runner = H.make_runner(d, dtype, page_size=64, num_pages=20, num_slots=2)
+            out = H.run_script(runner, seqs, script)
+            for i, ref in enumerate(refs):
+                H.check_rows(out[i], ref, dtype, f"medium {dtype} {name} seq {i}", f32_frac=4e-5)
