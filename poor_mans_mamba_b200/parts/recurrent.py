@@ -129,19 +129,22 @@ class GatedDeltaMixer(_StackedInput):
         c2 = c1 + self.gate_rank
         beta = proj[:, c2:c2 + self.heads]
         a = ws.alloc((T, self.heads * self.dim), proj.dtype)
-        streaming.linear(proj[:, c0:c1], self.a2, a, ctx)
         gate = ws.alloc((T, self.v_dim), proj.dtype)
-        # the output gate is needed only after the recurrence: its product runs beside the chain that
-        # leads there (a parallel branch of a recorded step)
+        # The second halves of the low-rank projections run beside the convolution (a parallel branch
+        # of a recorded step): the decays are needed by the recurrence, the output gate only after it.
         here = torch.cuda.current_stream(proj.device)
         side = branches.branch_stream(proj.device, "gate")
         with branches.fork(here, side):
+            streaming.linear(proj[:, c0:c1], self.a2, a, ctx)
+            decays_ready = torch.cuda.Event()
+            decays_ready.record(side)
             streaming.linear(proj[:, c1:c2], self.g2, gate, ctx)
         qkv = causal_conv(proj[:, :c0], self.conv_ones, None, self.conv_w, self.conv_w_t,
                           cache.fixed(f"{self.name}.conv"), ctx, activation=True)
         o = ws.alloc((T, self.v_dim), torch.float32)
         q, k, v = qkv[:, :self.qk_dim], qkv[:, self.qk_dim:2 * self.qk_dim], qkv[:, 2 * self.qk_dim:]
         state = cache.fixed(f"{self.name}.S")
+        here.wait_event(decays_ready)
         if _chunked(ctx, self.dim, True):
             scratch = ws.alloc((K.recurrent_chunked_scratch_floats(ctx.new_lens, self.heads, self.dim, self.vdim, True),),
                                torch.float32)
