@@ -19,6 +19,10 @@ tokens.  Prints ONE JSON line:
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from the stated
 fallback.  Inputs of a decode step (1 GB of weights plus the caches) exceed the L2, so no
 L2 flush is needed between timed iterations.
+
+`--workload compare` is a measurement beside the benchmark (its own JSON line): a Boketar model and a
+Falcon-H1 model of equal width, feed-forward size, layer count and vocabulary, one prompt step and
+decode steps of each with the L2 flushed before every timed step, and every kernel's device time.
 """
 from __future__ import annotations
 
