@@ -34,7 +34,7 @@ def batch_index(lens, slots):
 
 # ----------------------------------------------------------------------------- residual lanes
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n,D", [(1, 48), (2, 256), (3, 100), (8, 64)])
+@pytest.mark.parametrize("n,D", [(1, 48), (2, 256), (3, 100), (8, 64), (2, 77), (5, 50)])
 def test_lanes_mix_and_norm(dtype, n, D):
     T = 7
     x = rnd(n, T, D, seed=1)
