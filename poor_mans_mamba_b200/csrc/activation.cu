@@ -78,3 +78,63 @@ PMM_EXPORT int pmm_add_row_bias(void* x, const float* bias, int T, int D, int dt
                      pmm::add_row_bias_kernel<S><<<T, 256, 0, stream>>>(static_cast<S*>(x), bias, D));
   return pmm::launch_status();
 }
+
+namespace pmm {
+// out[t, h*dv + i] = scale * a[t, h*da + i] * sigmoid(g[t, h*dv + i]) for i < dv: an output gate per
+// channel on heads that may be stored wider (da >= dv) than they are used.
+template <typename S>
+__global__ void sigmoid_gate_kernel(const S* __restrict__ a, long long ld_a, const S* __restrict__ g, long long ld_g,
+                                    float scale, S* __restrict__ out, long long ld_o, int H, int da, int dv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int n = H * dv;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n; c += gridDim.y * blockDim.x) {
+    const int h = c / dv, i = c - h * dv;
+    const float gv = ldf(g + static_cast<long long>(t) * ld_g + c);
+    const float av = ldf(a + static_cast<long long>(t) * ld_a + h * da + i);
+    stf(out + static_cast<long long>(t) * ld_o + c, scale * av / (1.f + expf(-gv)));
+  }
+}
+
+// The clamped gated activation of a [gate | up] projection:
+//   g = min(gu[t, f], limit); u = clamp(gu[t, F + f], -limit, limit); out = g * sigmoid(alpha * g) * (u + shift)
+template <typename S>
+__global__ void clamped_glu_kernel(const S* __restrict__ gu, long long ld, float limit, float alpha, float shift,
+                                   S* __restrict__ out, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const S* row = gu + static_cast<long long>(t) * ld;
+  S* o = out + static_cast<size_t>(t) * F;
+  for (int f = blockIdx.y * blockDim.x + threadIdx.x; f < F; f += gridDim.y * blockDim.x) {
+    const float g = fminf(ldf(row + f), limit);
+    const float u = fminf(fmaxf(ldf(row + F + f), -limit), limit);
+    stf(o + f, g / (1.f + expf(-alpha * g)) * (u + shift));
+  }
+}
+}  // namespace pmm
+
+PMM_EXPORT int pmm_sigmoid_gate(const void* a, long long ld_a, const void* g, long long ld_g, float scale, void* out,
+                                long long ld_o, int T, int H, int da, int dv, int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || dv <= 0 || da < dv) return PMM_ERR_BAD_ARGUMENT;
+  int ytiles = (H * dv + 1023) / 1024;
+  if (ytiles > 64) ytiles = 64;
+  PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::sigmoid_gate_kernel<S>, dim3(T, ytiles), dim3(256), 0, stream,
+                                               static_cast<const S*>(a), ld_a, static_cast<const S*>(g), ld_g, scale,
+                                               static_cast<S*>(out), ld_o, H, da, dv));
+  return pmm::launch_status();
+}
+
+PMM_EXPORT int pmm_clamped_glu(const void* gu, long long ld, float limit, float alpha, float shift, void* out, int T,
+                               int F, int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (F <= 0) return PMM_ERR_BAD_ARGUMENT;
+  int ytiles = (F + 1023) / 1024;
+  if (ytiles > 64) ytiles = 64;
+  PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::clamped_glu_kernel<S>, dim3(T, ytiles), dim3(256), 0, stream,
+                                               static_cast<const S*>(gu), ld, limit, alpha, shift,
+                                               static_cast<S*>(out), F));
+  return pmm::launch_status();
+}

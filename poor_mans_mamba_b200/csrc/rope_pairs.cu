@@ -1,9 +1,11 @@
-// Rotation of neighbouring pairs on part of every head, and the write into the cache pages, for
-// heads whose key size d and value size dv differ.
+// Rotation on part of every head, and the write into the cache pages, for heads whose key size d and
+// value size dv differ.
 //
-// The first rot_dims entries of every query and key head are rotated pairwise: entries (2i, 2i+1)
-// at position p become (x cos a - y sin a, y cos a + x sin a) with a = p * inv_freq[i]; entries from
-// rot_dims on pass unchanged; values are not rotated.  Positions, angles, sines and cosines are
+// The first rot_dims entries of every query and key head are rotated in pairs (x, y): at position p they
+// become (x cos a - y sin a, y cos a + x sin a) with a = p * inv_freq[i].  Pair i is entries (2i, 2i+1)
+// (neighbouring pairs) or entries (i, i + rot_dims/2) (half layout: the first half of the rotated
+// part against its second half); entries from rot_dims on pass unchanged; values are not rotated.
+// A bias per channel (float, optional) is added to q, k and v as they are read.  Positions, angles, sines and cosines are
 // float.  Queries go to q_out [T, H*Dp], keys and values into their page
 // [page, plane, page_size, G*Dp]: all heads are laid out Dp = max(d, dv) rounded up wide, padded
 // with zeros, so that one attention kernel of head size Dp serves both sizes (zeros add nothing to
@@ -14,14 +16,18 @@
 namespace pmm {
 
 template <typename S>
-__device__ __forceinline__ float rotated(const S* __restrict__ head, int i, int rot_dims, float pos,
-                                         const float* __restrict__ inv_freq) {
-  const float x = ldf(head + i);
+__device__ __forceinline__ float rotated(const S* __restrict__ head, const float* __restrict__ bias, int i, int rot_dims,
+                                         float pos, const float* __restrict__ inv_freq, int half_layout) {
+  const float x = ldf(head + i) + (bias ? bias[i] : 0.f);
   if (i >= rot_dims) return x;
-  const float other = ldf(head + (i ^ 1));
+  const int half = rot_dims >> 1;
+  const bool second = half_layout ? i >= half : (i & 1);
+  const int j = half_layout ? (second ? i - half : i + half) : (i ^ 1);
+  const int f = half_layout ? (second ? i - half : i) : (i >> 1);
+  const float other = ldf(head + j) + (bias ? bias[j] : 0.f);
   float sn, cs;
-  sincosf(pos * inv_freq[i >> 1], &sn, &cs);
-  return (i & 1) ? x * cs + other * sn : x * cs - other * sn;
+  sincosf(pos * inv_freq[f], &sn, &cs);
+  return second ? x * cs + other * sn : x * cs - other * sn;
 }
 
 template <typename S>
@@ -31,7 +37,8 @@ __global__ void __launch_bounds__(256)
                             const int* __restrict__ positions, const int* __restrict__ seq_of,
                             const int* __restrict__ block_table, int max_blocks, S* __restrict__ pool,
                             int page_size, S* __restrict__ q_out, int H, int G, int d, int dv, int Dp,
-                            int rot_dims) {
+                            int rot_dims, int half_layout, const float* __restrict__ q_bias,
+                            const float* __restrict__ k_bias, const float* __restrict__ v_bias) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -44,15 +51,17 @@ __global__ void __launch_bounds__(256)
   for (int e = threadIdx.x; e < n_q + 2 * n_kv; e += blockDim.x) {
     if (e < n_q) {
       const int h = e / Dp, i = e - h * Dp;
-      const float val = i < d ? rotated(q + static_cast<long long>(t) * ld_q + h * d, i, rot_dims, fpos, inv_freq) : 0.f;
+      const float val = i < d ? rotated(q + static_cast<long long>(t) * ld_q + h * d, q_bias ? q_bias + h * d : nullptr, i, rot_dims,
+                                        fpos, inv_freq, half_layout) : 0.f;
       stf(q_out + static_cast<size_t>(t) * n_q + e, val);
     } else if (e < n_q + n_kv) {
       const int c = e - n_q, g = c / Dp, i = c - g * Dp;
-      const float val = i < d ? rotated(k + static_cast<long long>(t) * ld_k + g * d, i, rot_dims, fpos, inv_freq) : 0.f;
+      const float val = i < d ? rotated(k + static_cast<long long>(t) * ld_k + g * d, k_bias ? k_bias + g * d : nullptr, i, rot_dims,
+                                        fpos, inv_freq, half_layout) : 0.f;
       stf(k_row + c, val);
     } else {
       const int c = e - n_q - n_kv, g = c / Dp, i = c - g * Dp;
-      stf(v_row + c, i < dv ? ldf(v + static_cast<long long>(t) * ld_v + g * dv + i) : 0.f);
+      stf(v_row + c, i < dv ? ldf(v + static_cast<long long>(t) * ld_v + g * dv + i) + (v_bias ? v_bias[g * dv + i] : 0.f) : 0.f);
     }
   }
 }
@@ -60,11 +69,13 @@ __global__ void __launch_bounds__(256)
 }  // namespace pmm
 
 // q [T, H*d], k [T, G*d], v [T, G*dv] rows of stride ld; inv_freq [rot_dims/2] floats (may be nullptr when
-// rot_dims is 0); pool [pages, 2, page_size, G*Dp]; q_out [T, H*Dp].
+// rot_dims is 0); pool [pages, 2, page_size, G*Dp]; q_out [T, H*Dp]; q_bias [H*d], k_bias [G*d], v_bias [G*dv]
+// floats or nullptr.
 PMM_EXPORT int pmm_rope_pairs_store(const void* q, long long ld_q, const void* k, long long ld_k, const void* v,
                                     long long ld_v, const float* inv_freq, const int* positions, const int* seq_of,
                                     const int* block_table, int max_blocks, void* pool, int page_size, void* q_out,
-                                    int T, int H, int G, int d, int dv, int Dp, int rot_dims, int dtype,
+                                    int T, int H, int G, int d, int dv, int Dp, int rot_dims, int half_layout,
+                                    const float* q_bias, const float* k_bias, const float* v_bias, int dtype,
                                     cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || G <= 0 || d <= 0 || dv <= 0 || Dp < d || Dp < dv || rot_dims < 0 || rot_dims > d || rot_dims % 2 ||
@@ -74,6 +85,7 @@ PMM_EXPORT int pmm_rope_pairs_store(const void* q, long long ld_q, const void* k
                                                static_cast<const S*>(q), ld_q, static_cast<const S*>(k), ld_k,
                                                static_cast<const S*>(v), ld_v, inv_freq, positions, seq_of,
                                                block_table, max_blocks, static_cast<S*>(pool), page_size,
-                                               static_cast<S*>(q_out), H, G, d, dv, Dp, rot_dims));
+                                               static_cast<S*>(q_out), H, G, d, dv, Dp, rot_dims, half_layout, q_bias,
+                                               k_bias, v_bias));
   return pmm::launch_status();
 }

@@ -67,7 +67,7 @@ _SIGNATURES = {
                        c_void_p],
     "pmm_rope_pairs_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                             c_int, c_int, c_int, c_void_p],
+                             c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "pmm_delta_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
                        c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                        c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
@@ -111,6 +111,18 @@ _SIGNATURES = {
                     c_void_p, c_void_p],
     "pmm_silu_mul": [c_void_p, c_longlong, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_add_row_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "pmm_add_tanh_norm": [c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "pmm_sigmoid_gate": [c_void_p, c_longlong, c_void_p, c_longlong, c_float, c_void_p, c_longlong, c_int, c_int, c_int,
+                         c_int, c_int, c_void_p],
+    "pmm_clamped_glu": [c_void_p, c_longlong, c_float, c_float, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+    "pmm_moe_route": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                      c_void_p],
+    "pmm_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "pmm_moe_tile_rows": [c_int],
+    "pmm_moe_gemm": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                     c_int, c_float, c_float, c_float, c_void_p, c_int, c_int, c_void_p],
+    "pmm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                         c_void_p, c_void_p, c_void_p],
 }
@@ -403,6 +415,63 @@ def add_rmsnorm(h: Tensor, branches: Sequence[Tuple[Tensor, float]], weight: Opt
         return  # nothing to add and nothing to write
     _call("pmm_add_rmsnorm", h.data_ptr(), ptrs[0], scales[0], ptrs[1], scales[1], _ptr(weight),
           float(eps), _ptr(out), _ptr(rows), R, D, dtype, _stream())
+
+
+def add_tanh_norm(h: Optional[Tensor], branches: Sequence[Tuple[Tensor, float]],
+                  post: Optional[Tuple[Tensor, Tensor, Tensor]], pre: Optional[Tuple[Tensor, Tensor, Tensor]],
+                  out: Optional[Tensor], rows: Optional[Tensor] = None) -> None:
+    """The norm y = tanh(alpha x) * w + b with the residual fold.  s = s0*b0 + s1*b1; with ``post``
+    (alpha, w, b) s <- post(s); h <- h + s (rows is None); with ``pre`` (alpha, w, b) out = pre(h).
+    h None: out = pre(s).  With ``rows`` h is left as it is and out[r] comes from row rows[r].
+    alpha is a tensor of one float."""
+    _cuda(h, out, rows)
+    ref = h if h is not None else (branches[0][0] if branches else None)
+    if ref is None or ref.dim() != 2:
+        raise KernelError("add_tanh_norm: needs a stream or a branch [T, D]")
+    T, D = ref.shape
+    if h is not None and not (h.dtype == torch.float32 and h.is_contiguous()):
+        raise KernelError("add_tanh_norm: the residual stream must be contiguous float32 [T, D]")
+    if len(branches) > 2:
+        raise KernelError("add_tanh_norm: at most two branches")
+    ptrs: List[Optional[int]] = [None, None]
+    scales = [0.0, 0.0]
+    dtype = None
+    for i, (b, s) in enumerate(branches):
+        _cuda(b)
+        if not (b.shape == (T, D) and b.is_contiguous()):
+            raise KernelError("add_tanh_norm: branch must be contiguous [T, D]")
+        ptrs[i], scales[i] = b.data_ptr(), float(s)
+        dtype = _dt(b) if dtype is None else dtype
+        if _dt(b) != dtype:
+            raise KernelError("add_tanh_norm: branches of different storage types")
+    trios = []
+    for trio, what in ((post, "post"), (pre, "pre")):
+        if trio is None:
+            trios += [None, None, None]
+            continue
+        al, w, b = trio
+        _cuda(al, w, b)
+        _f32vec(w, D, f"add_tanh_norm: {what} weight")
+        _f32vec(b, D, f"add_tanh_norm: {what} bias")
+        if not (al.dtype == torch.float32 and al.numel() == 1):
+            raise KernelError(f"add_tanh_norm: {what} alpha must be one float")
+        trios += [al.data_ptr(), w.data_ptr(), b.data_ptr()]
+    R = T
+    if rows is not None:
+        _i32(rows, "add_tanh_norm: rows")
+        R = rows.numel()
+    if out is not None:
+        if pre is None:
+            raise KernelError("add_tanh_norm: an output needs the norm's tensors")
+        if not (out.shape == (R, D) and out.is_contiguous()):
+            raise KernelError("add_tanh_norm: out must be contiguous [rows, D]")
+        if not (dtype is None or _dt(out) == dtype):
+            raise KernelError("add_tanh_norm: out and branches differ in storage type")
+        dtype = _dt(out)
+    if dtype is None:
+        return
+    _call("pmm_add_tanh_norm", _ptr(h), ptrs[0], scales[0], ptrs[1], scales[1], trios[0], trios[1], trios[2], trios[3],
+          trios[4], trios[5], _ptr(out), _ptr(rows), R, D, dtype, _stream())
 
 
 def scale_f32_(x: Tensor, s: float) -> None:
@@ -1325,6 +1394,111 @@ def silu_mul(gate_up: Tensor, gate_mult: float, out: Tensor) -> None:
           _dt(gate_up), _stream())
 
 
+def sigmoid_gate(a: Tensor, g: Tensor, scale: float, out: Tensor, n_heads: int, stored_dim: int, dim: int) -> None:
+    """out[t, h*dim + i] = scale * a[t, h*stored_dim + i] * sigmoid(g[t, h*dim + i]) for i < dim."""
+    _cuda(a, g, out)
+    T = a.shape[0]
+    if not (a.shape == (T, n_heads * stored_dim) and g.shape == (T, n_heads * dim) and out.shape == (T, n_heads * dim)
+            and a.dtype == g.dtype == out.dtype and stored_dim >= dim):
+        raise KernelError("sigmoid_gate: a [T, H*stored], g and out [T, H*dim] of one type")
+    ld_a, ld_g, ld_o = (_rows_view(t, "sigmoid_gate") for t in (a, g, out))
+    _call("pmm_sigmoid_gate", a.data_ptr(), ld_a, g.data_ptr(), ld_g, float(scale), out.data_ptr(), ld_o, T, n_heads,
+          stored_dim, dim, _dt(a), _stream())
+
+
+def clamped_glu(gate_up: Tensor, limit: float, alpha: float, shift: float, out: Tensor) -> None:
+    """out = g * sigmoid(alpha g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit),
+    [gate | up] = gate_up [T, 2F]."""
+    _cuda(gate_up, out)
+    T, F2 = gate_up.shape
+    if not (F2 % 2 == 0 and out.shape == (T, F2 // 2) and out.is_contiguous() and out.dtype == gate_up.dtype):
+        raise KernelError("clamped_glu: gate_up [T, 2F], out contiguous [T, F] of the same type")
+    _call("pmm_clamped_glu", gate_up.data_ptr(), _rows_view(gate_up, "clamped_glu"), float(limit), float(alpha),
+          float(shift), out.data_ptr(), T, F2 // 2, _dt(out), _stream())
+
+
+# ----------------------------------------------------------------------------- routed feed-forward
+def moe_route(x: Tensor, router_w: Tensor, router_b: Optional[Tensor], top: int, ids: Tensor, weights: Tensor) -> None:
+    """ids, weights [T, top]: the ``top`` largest of x Wr^T + br (float arithmetic) and their softmax."""
+    _cuda(x, router_w, router_b, ids, weights)
+    T, D = x.shape
+    E = router_w.shape[0]
+    if not (router_w.shape == (E, D) and router_w.dtype == torch.float32 and router_w.is_contiguous()):
+        raise KernelError("moe_route: router weight [E, D] float32")
+    if router_b is not None:
+        _f32vec(router_b, E, "moe_route: router bias")
+    if not (ids.shape == (T, top) and ids.dtype == torch.int32 and ids.is_contiguous() and weights.shape == (T, top)
+            and weights.dtype == torch.float32 and weights.is_contiguous() and 1 <= top <= E):
+        raise KernelError("moe_route: ids int32 and weights float32, both contiguous [T, top], top <= experts")
+    _call("pmm_moe_route", x.data_ptr(), _rows_view(x, "moe_route"), router_w.data_ptr(), _ptr(router_b), ids.data_ptr(),
+          weights.data_ptr(), T, D, E, int(top), _dt(x), _stream())
+
+
+def moe_tile_rows(tensor_cores: bool) -> int:
+    return int(_fn("pmm_moe_tile_rows")(int(bool(tensor_cores))))
+
+
+def moe_row_tiles(n_pairs: int, n_experts: int, tensor_cores: bool) -> int:
+    """Upper bound of the row tiles of a plan over ``n_pairs`` (token, choice) pairs."""
+    return n_pairs // moe_tile_rows(tensor_cores) + min(n_experts, n_pairs)
+
+
+def moe_plan(ids: Tensor, n_experts: int, tensor_cores: bool, offsets: Tensor, tile_start: Tensor, perm: Tensor) -> None:
+    """Sorts the pairs by expert: offsets, tile_start [E + 1] int32, perm [T * top] int32."""
+    _cuda(ids, offsets, tile_start, perm)
+    A = ids.numel()
+    for t, n, what in ((offsets, n_experts + 1, "offsets"), (tile_start, n_experts + 1, "tile_start"), (perm, A, "perm")):
+        if not (t.dtype == torch.int32 and t.is_contiguous() and t.numel() == n):
+            raise KernelError(f"moe_plan: {what} must be contiguous int32 of {n}")
+    _i32(ids, "moe_plan: ids")
+    _call("pmm_moe_plan", ids.data_ptr(), A, int(n_experts), moe_tile_rows(tensor_cores), offsets.data_ptr(),
+          tile_start.data_ptr(), perm.data_ptr(), _stream())
+    global launch_count
+    launch_count += 1  # two launches
+
+
+def moe_gemm_tc_ok(a: Tensor, w: Tensor) -> bool:
+    """Whether the grouped product of these operands can run on the tensor cores."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.stride(1) == 1
+            and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def moe_gemm(a: Tensor, w: Tensor, perm: Tensor, offsets: Tensor, tile_start: Tensor, top: int, up: bool, out: Tensor,
+             tensor_cores: bool, limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0) -> None:
+    """Grouped product over the rows of a plan.  ``up``: a = x [T, K], w [E, 2N, K] ([gate | up] rows of
+    every expert), out = act [T*top, N] in the storage type, with the clamped gated activation.  Else:
+    a = act [T*top, K], w [E, N, K], out = y [T*top, N] float32 in the order of the pairs."""
+    _cuda(a, w, perm, offsets, tile_start, out)
+    A = perm.numel()
+    E = w.shape[0]
+    K = a.shape[1]
+    N = out.shape[1]
+    if not (w.dim() == 3 and w.is_contiguous() and w.shape == (E, (2 if up else 1) * N, K) and w.dtype == a.dtype):
+        raise KernelError("moe_gemm: w must be contiguous [E, N (2N for the gate and up rows), K] of a's type")
+    if not (out.shape == (A, N) and out.is_contiguous() and out.dtype == (a.dtype if up else torch.float32)):
+        raise KernelError("moe_gemm: out [pairs, N], the storage type for the activation, float32 for the result")
+    if not (a.shape[0] == (A // top if up else A) and offsets.numel() == E + 1 and tile_start.numel() == E + 1):
+        raise KernelError("moe_gemm: rows of a, offsets or tile_start do not fit the plan")
+    if tensor_cores and not moe_gemm_tc_ok(a, w):
+        raise KernelError("moe_gemm: the tensor-core form needs bfloat16, K a multiple of 8 and 16-byte aligned rows")
+    _call("pmm_moe_gemm", a.data_ptr(), _rows_view(a, "moe_gemm"), w.data_ptr(), perm.data_ptr(), offsets.data_ptr(),
+          tile_start.data_ptr(), A, E, int(top), K, N, int(bool(up)), float(limit), float(alpha), float(shift),
+          out.data_ptr(), int(bool(tensor_cores)), _dt(a), _stream())
+
+
+def moe_combine(y: Tensor, weights: Tensor, shared: Optional[Tensor], out: Tensor) -> None:
+    """out[t] = sum_j weights[t, j] * y[t*top + j] (+ shared[t])."""
+    _cuda(y, weights, shared, out)
+    T, top = weights.shape
+    D = out.shape[1]
+    if not (y.shape == (T * top, D) and y.dtype == torch.float32 and y.is_contiguous() and out.shape == (T, D)
+            and out.is_contiguous() and weights.dtype == torch.float32 and weights.is_contiguous()):
+        raise KernelError("moe_combine: y [T*top, D] float32, weights [T, top] float32, out contiguous [T, D]")
+    if shared is not None and not (shared.shape == (T, D) and shared.is_contiguous() and shared.dtype == out.dtype):
+        raise KernelError("moe_combine: shared must be contiguous [T, D] of out's type")
+    _call("pmm_moe_combine", y.data_ptr(), weights.data_ptr(), _ptr(shared), out.data_ptr(), T, D, top, _dt(out), _stream())
+
+
 def add_row_bias_(x: Tensor, bias: Tensor) -> None:
     """x[t, :] += bias (float32 vector) for a contiguous [T, D] activation."""
     _cuda(x, bias)
@@ -1478,11 +1652,19 @@ def normed_sum(branches: Sequence[Tuple[Tensor, Tensor]], eps: float, scale: flo
 # ----------------------------------------------------------------------------- pair rotation + page write
 def rope_pairs_store(q: Tensor, k: Tensor, v: Tensor, inv_freq: Optional[Tensor], rot_dims: int, positions: Tensor,
                      seq_of: Tensor, block_table: Tensor, pool: Tensor, q_out: Tensor, n_heads: int,
-                     n_kv_heads: int, dim: int, vdim: int, padded_dim: int) -> None:
-    """Rotates neighbouring pairs of the first ``rot_dims`` entries of every query and key head,
-    writes queries to q_out [T, H*Dp] and keys and values into their pages [pages, 2, page, G*Dp],
-    every head padded with zeros to Dp = ``padded_dim`` entries."""
+                     n_kv_heads: int, dim: int, vdim: int, padded_dim: int, half_layout: bool = False,
+                     biases: Optional[Tuple[Tensor, Tensor, Tensor]] = None) -> None:
+    """Rotates pairs among the first ``rot_dims`` entries of every query and key head (neighbours
+    (2i, 2i+1), or with ``half_layout`` entries (i, i + rot_dims/2)), writes queries to q_out [T, H*Dp]
+    and keys and values into their pages [pages, 2, page, G*Dp], every head padded with zeros to Dp =
+    ``padded_dim`` entries.  ``biases``: float vectors added to q, k and v as they are read."""
     _cuda(q, k, v, inv_freq, positions, seq_of, block_table, pool, q_out)
+    qb = kb = vb = None
+    if biases is not None:
+        qb, kb, vb = biases
+        _f32vec(qb, n_heads * dim, "rope_pairs_store: q bias")
+        _f32vec(kb, n_kv_heads * dim, "rope_pairs_store: k bias")
+        _f32vec(vb, n_kv_heads * vdim, "rope_pairs_store: v bias")
     T = q.shape[0]
     ld_q, ld_k, ld_v = (_rows_view(t, "rope_pairs_store") for t in (q, k, v))
     if not (q.shape[1] == n_heads * dim and k.shape == (T, n_kv_heads * dim) and v.shape == (T, n_kv_heads * vdim)
@@ -1498,8 +1680,8 @@ def rope_pairs_store(q: Tensor, k: Tensor, v: Tensor, inv_freq: Optional[Tensor]
     _i32(block_table, "rope_pairs_store: block_table")
     _call("pmm_rope_pairs_store", q.data_ptr(), ld_q, k.data_ptr(), ld_k, v.data_ptr(), ld_v, _ptr(inv_freq),
           positions.data_ptr(), seq_of.data_ptr(), block_table.data_ptr(), block_table.shape[1], pool.data_ptr(),
-          pool.shape[2], q_out.data_ptr(), T, n_heads, n_kv_heads, dim, vdim, padded_dim, int(rot_dims), _dt(q),
-          _stream())
+          pool.shape[2], q_out.data_ptr(), T, n_heads, n_kv_heads, dim, vdim, padded_dim, int(rot_dims),
+          int(bool(half_layout)), _ptr(qb), _ptr(kb), _ptr(vb), _dt(q), _stream())
 
 
 # ----------------------------------------------------------------------------- matrix-state recurrences

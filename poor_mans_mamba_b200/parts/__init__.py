@@ -9,4 +9,5 @@ from .base import (FeedForward, LayerCache, LayerCall, LayerSpec, Mixer, ModelSp
 from . import streaming  # noqa: F401
 from . import norm, rope, ffn, attention, mamba2, block  # noqa: F401  (registration)
 from . import hyper, parallel, recurrent, window_attention  # noqa: F401  (registration)
+from . import gated_attention, moe  # noqa: F401  (registration)
 from .block import ParallelPreNormBlock, ResidualStream, prenorm_layer

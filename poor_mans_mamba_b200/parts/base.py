@@ -117,6 +117,23 @@ class Norm(Part):
     def forward(self, h: Tensor, pending, out: Tensor, rows: Optional[Tensor], ctx) -> None:
         raise NotImplementedError
 
+    # A sublayer's result may be normed once more before it joins the stream (a *post* norm).  The
+    # stream keeps such a result pending together with its post norm; the norm of the next sublayer's
+    # input folds both in one launch where it can (``folds_post``), else the post norm is applied by a
+    # launch of its own (``apply``) and the result waits as an ordinary branch.
+    def folds_post(self, post: "Norm") -> bool:
+        """Whether `forward(..., post=post)` applies ``post`` to the sum of the pending branches itself."""
+        return False
+
+    def apply(self, pending, out: Tensor, ctx) -> None:
+        """out = norm(sum of scale_i * branch_i), without a stream."""
+        raise NotImplementedError(f"{type(self).__name__} cannot norm a sublayer's result")
+
+    def fold(self, h: Tensor, pending, ctx) -> None:
+        """h <- h + norm(sum of scale_i * branch_i): this norm as the post norm of branches that join
+        the stream with no norm of the stream following."""
+        raise NotImplementedError(f"{type(self).__name__} cannot norm a sublayer's result")
+
     def rms_prologue(self) -> Optional[Tuple[Tensor, float]]:
         """(weight [D] float32, eps) if this norm is y = x / sqrt(mean(x^2) + eps) * weight, which
         the weight-streaming products of few-token steps can apply in their prologue; None for any

@@ -13,7 +13,7 @@ writes the stream once.
 from __future__ import annotations
 
 import os
-from typing import List, Optional, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 
@@ -32,10 +32,17 @@ _PARALLEL_MIXERS = os.environ.get("PMM_PARALLEL_MIXERS", "1") == "1"
 
 
 def prenorm_layer(prefix: str, mixer_norm: PartSpec, mixers, ffn_norm: Optional[PartSpec] = None,
-                  ffn: Optional[PartSpec] = None) -> LayerSpec:
-    """The LayerSpec of a ``parallel_prenorm`` layer: norm -> parallel mixers -> norm -> feed-forward."""
-    return LayerSpec("parallel_prenorm", prefix, {"mixer_norm": mixer_norm, "mixers": tuple(mixers),
-                                                  "ffn_norm": ffn_norm, "ffn": ffn})
+                  ffn: Optional[PartSpec] = None, mixer_post_norm: Optional[PartSpec] = None,
+                  ffn_post_norm: Optional[PartSpec] = None) -> LayerSpec:
+    """The LayerSpec of a ``parallel_prenorm`` layer: norm -> parallel mixers -> norm -> feed-forward.
+    With post norms each sublayer's result is normed once more before it joins the stream:
+    x <- x + post(sum of the scaled mixers' outputs), x <- x + post(feed-forward)."""
+    parts = {"mixer_norm": mixer_norm, "mixers": tuple(mixers), "ffn_norm": ffn_norm, "ffn": ffn}
+    if mixer_post_norm is not None:
+        parts["mixer_post_norm"] = mixer_post_norm
+    if ffn_post_norm is not None:
+        parts["ffn_post_norm"] = ffn_post_norm
+    return LayerSpec("parallel_prenorm", prefix, parts)
 
 
 _LANE_ONES = {}
@@ -55,6 +62,7 @@ class ResidualStream:
         self.h = h
         self.ctx = ctx
         self.pending: List[Tuple[Tensor, float]] = []
+        self.pending_post: Optional[Norm] = None  # normed once more before the pending branches join (see Norm.folds_post)
         self._buffers = [ctx.workspace.alloc(tuple(h.shape), ctx.dtype) for _ in range(n_branch_buffers)]
         self._taken = 0
         # Residual state in lanes [n, T, D] (see ModelSpec.residual_lanes): every lane starts as h, so
@@ -76,7 +84,25 @@ class ResidualStream:
         return buf
 
     def add(self, branch: Tensor, scale: float) -> None:
+        if self.pending_post is not None:
+            self._settle_post()  # what waits with a post norm is one sublayer's result: settle it first
         self.pending.append((branch, float(scale)))
+
+    def add_normed(self, branches: Sequence[Tuple[Tensor, float]], post: Norm) -> None:
+        """A sublayer's result sum(scale_i * branch_i) waits to join the stream as post(that sum)."""
+        if self.pending:
+            self.flush()
+        self.pending = [(b, float(s)) for b, s in branches]
+        self.pending_post = post
+
+    def _settle_post(self) -> None:
+        """Apply the waiting post norm by a launch of its own; its result waits as an ordinary branch."""
+        post, self.pending_post = self.pending_post, None
+        if post is None or not self.pending:
+            return
+        out = self.take_branch()  # (arrangements with post norms ask for one buffer more)
+        post.apply(self.pending, out, self.ctx)
+        self.pending = [(out, 1.0)]
 
     def lane_add(self, y: Tensor, mix: Tensor, out_w: Tensor) -> None:
         """A sublayer's result waits to enter the lanes: x_t <- sum_s mix[s, t] x_s + out_w[t] y."""
@@ -110,17 +136,26 @@ class ResidualStream:
             return self.lanes_normed(self._ones, norm, rows)
         n_rows = self.h.shape[0] if rows is None else rows.numel()
         out = self.ctx.workspace.alloc((n_rows, self.h.shape[1]), self.ctx.dtype)
-        norm.forward(self.h, self.pending, out, rows, self.ctx)
+        if self.pending_post is not None and self.pending and norm.folds_post(self.pending_post):
+            norm.forward(self.h, self.pending, out, rows, self.ctx, post=self.pending_post)
+        else:
+            self._settle_post()
+            norm.forward(self.h, self.pending, out, rows, self.ctx)
         if rows is None:
             self.pending = []
+            self.pending_post = None
             self._taken = 0
         return out
 
     def flush(self) -> Tensor:
         if self.lanes is not None:
             raise RuntimeError("a residual state in lanes has no single stream to flush into")
-        fold_branches(self.h, self.pending)
+        if self.pending_post is not None and self.pending:
+            self.pending_post.fold(self.h, self.pending, self.ctx)
+        else:
+            fold_branches(self.h, self.pending)
         self.pending = []
+        self.pending_post = None
         self._taken = 0
         return self.h
 
@@ -129,30 +164,42 @@ class ParallelPreNormBlock(Part):
     def __init__(self, spec: LayerSpec, hidden_size: int):
         self.prefix = spec.prefix
         self.hidden_size = hidden_size
-        unknown = set(spec.parts) - {"mixer_norm", "mixers", "ffn_norm", "ffn"}
+        unknown = set(spec.parts) - {"mixer_norm", "mixers", "ffn_norm", "ffn", "mixer_post_norm", "ffn_post_norm"}
         if unknown or spec.part("mixer_norm") is None or not spec.part("mixers"):
-            raise ValueError("parallel_prenorm takes the parts mixer_norm, mixers (at least one), ffn_norm and ffn"
-                             + (f"; got also {sorted(unknown)}" if unknown else ""))
+            raise ValueError("parallel_prenorm takes the parts mixer_norm, mixers (at least one), ffn_norm, ffn, "
+                             "mixer_post_norm and ffn_post_norm" + (f"; got also {sorted(unknown)}" if unknown else ""))
         self.mixer_norm: Norm = build_part("norm", spec.part("mixer_norm"), width=hidden_size)
         self.mixers: List[Mixer] = [build_part("mixer", m, hidden_size=hidden_size) for m in spec.part("mixers")]
+        self.mixer_post_norm: Optional[Norm] = None
+        if spec.part("mixer_post_norm") is not None:
+            self.mixer_post_norm = build_part("norm", spec.part("mixer_post_norm"), width=hidden_size)
         self.ffn_norm: Optional[Norm] = None
         self.ffn: Optional[FeedForward] = None
+        self.ffn_post_norm: Optional[Norm] = None
         if spec.part("ffn") is not None:
             if spec.part("ffn_norm") is None:
                 raise ValueError("a feed-forward needs its norm")
             self.ffn_norm = build_part("norm", spec.part("ffn_norm"), width=hidden_size)
             self.ffn = build_part("feed_forward", spec.part("ffn"), hidden_size=hidden_size)
+            if spec.part("ffn_post_norm") is not None:
+                self.ffn_post_norm = build_part("norm", spec.part("ffn_post_norm"), width=hidden_size)
         self._fused_in: Optional[Tensor] = None
         self._fused_cols: List[Tuple[int, int]] = []
 
     def parts(self) -> List[Part]:
         out: List[Part] = [self.mixer_norm, *self.mixers]
+        if self.mixer_post_norm is not None:
+            out.append(self.mixer_post_norm)
         if self.ffn is not None:
             out += [self.ffn_norm, self.ffn]
+            if self.ffn_post_norm is not None:
+                out.append(self.ffn_post_norm)
         return out
 
     def branch_buffers_needed(self) -> int:
-        return max(len(self.mixers), 1)
+        # with post norms a sublayer's result may still wait while the next one takes its buffer
+        extra = 1 if (self.mixer_post_norm is not None or self.ffn_post_norm is not None) else 0
+        return max(len(self.mixers), 1) + extra
 
     def state_specs(self) -> List[Tuple[str, StateSpec]]:
         """(qualified name, spec) for every state of every mixer of this layer."""
@@ -180,6 +227,8 @@ class ParallelPreNormBlock(Part):
         (a feed-forward without a few-token path of its own runs its general `forward`)."""
         if not streaming.eligible(ctx, self.hidden_size) or self._fused_in is None:
             return False
+        if self.mixer_post_norm is not None or self.ffn_post_norm is not None:
+            return False  # the products of that path add straight into the stream
         if any(m.output_weight() is None or m.output_bias() is not None for m in self.mixers):
             return False
         return len(self.mixers) <= 2
@@ -261,7 +310,10 @@ class ParallelPreNormBlock(Part):
         n = stream.normed(self.mixer_norm)
         if self._fused_in is not None:
             proj = ws.alloc((n.shape[0], self._fused_in.shape[0]), n.dtype)
-            K.linear(n, self._fused_in, proj)
+            if self.mixer_post_norm is not None:
+                streaming.linear(n, self._fused_in, proj, ctx)  # (few tokens: the weight-streaming product)
+            else:
+                K.linear(n, self._fused_in, proj)
             # The mixers only share their input.  With several, the first runs on a side stream
             # beside the others (parallel branches of a captured step): a prompt portion's scan and
             # attention are each a chain of launches with few blocks, and together they fill the GPU.
@@ -276,18 +328,25 @@ class ParallelPreNormBlock(Part):
                     m.forward_projected(proj[:, c0:c1], ctx, cache, outs[i])
             if side is not None:
                 main.wait_stream(side)
-            for m, out in zip(self.mixers, outs):
-                stream.add(out, m.out_scale)
         else:
+            outs = []
             for m in self.mixers:
-                out = stream.take_branch()
-                m.forward(n, ctx, cache, out)
-                stream.add(out, m.out_scale)
+                outs.append(stream.take_branch())
+                m.forward(n, ctx, cache, outs[-1])
+        results = [(out, m.out_scale) for m, out in zip(self.mixers, outs)]
+        if self.mixer_post_norm is not None:
+            stream.add_normed(results, self.mixer_post_norm)
+        else:
+            for out, scale in results:
+                stream.add(out, scale)
         if self.ffn is not None:
             f = stream.normed(self.ffn_norm)
             out = stream.take_branch()
             self.ffn.forward(f, ctx, out)
-            stream.add(out, self.ffn.out_scale)
+            if self.ffn_post_norm is not None:
+                stream.add_normed([(out, self.ffn.out_scale)], self.ffn_post_norm)
+            else:
+                stream.add(out, self.ffn.out_scale)
         ws.release(mark)
 
 

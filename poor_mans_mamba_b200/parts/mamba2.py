@@ -47,11 +47,15 @@ class Mamba2Mixer(Mixer):
                  n_groups: int, chunk_size: int = 128, conv_bias: bool = True, proj_bias: bool = False,
                  gated_norm: bool = False, norm_before_gate: bool = False, norm_eps: float = 1e-5,
                  in_multiplier: float = 1.0, out_multiplier: float = 1.0,
-                 chunk_multipliers: Sequence[float] = (1.0, 1.0, 1.0, 1.0, 1.0)):
+                 chunk_multipliers: Sequence[float] = (1.0, 1.0, 1.0, 1.0, 1.0), norm_groups: Optional[int] = None,
+                 tensors: Optional[Dict[str, str]] = None):
+        """``norm_groups``: the number of equal parts the gated norm takes its root mean square over
+        (default: ``n_groups``).  ``tensors``: other names for this part's tensors, keyed by the names
+        of `param_specs` (e.g. {"in_proj.weight": "in", "conv1d.bias": "conv.b"})."""
         if n_heads % n_groups:
             raise ValueError("n_heads must be divisible by n_groups")
-        if d_conv < 2:
-            raise ValueError("d_conv must be at least 2")
+        if d_conv < 1:
+            raise ValueError("d_conv must be at least 1")
         if d_state > 256:
             raise ValueError(f"the scan kernels take d_state up to 256, got {d_state}")
         if len(chunk_multipliers) != 5:
@@ -68,35 +72,45 @@ class Mamba2Mixer(Mixer):
         self.in_multiplier = float(in_multiplier)
         self.out_scale = float(out_multiplier)
         self.chunk_multipliers = tuple(float(m) for m in chunk_multipliers)
+        self.norm_groups = int(norm_groups) if norm_groups is not None else self.n_groups
+        if self.gated_norm and (self.norm_groups <= 0 or self.d_ssm % self.norm_groups):
+            raise ValueError("the gated norm's parts must divide the inner width")
+        self.tensor_names = dict(tensors or {})
         self.w_in: Optional[Tensor] = None
+
+    def _t(self, name: str) -> str:
+        return self.tensor_names.get(name, name)
 
     # -- tensors and state
     def param_specs(self) -> List[ParamSpec]:
         h, c, k = self.n_heads, self.conv_dim, self.d_conv
+        t = self._t
+        renamed = bool(self.tensor_names)  # under other names the convolution is stored [C, K] as it is used
         specs = [
-            ParamSpec("in_proj.weight", (self.proj_dim, self.hidden_size)),
-            ParamSpec("conv1d.weight", (c, k), kind="vector", alt_shapes=((c, 1, k),), stored_shape=(c, 1, k)),
-            ParamSpec("A_log", (h,), kind="vector", init=("log_uniform", 1.0, 16.0)),
-            ParamSpec("D", (h,), kind="vector", init=("ones",)),
-            ParamSpec("dt_bias", (h,), kind="vector", init=("inv_softplus_log_uniform", 1e-3, 0.1)),
-            ParamSpec("out_proj.weight", (self.hidden_size, self.d_ssm)),
+            ParamSpec(t("in_proj.weight"), (self.proj_dim, self.hidden_size)),
+            ParamSpec(t("conv1d.weight"), (c, k), kind="vector", alt_shapes=((c, 1, k),),
+                      stored_shape=(c, k) if renamed else (c, 1, k), init=("normal", 0.5) if renamed else ("normal", 0.02)),
+            ParamSpec(t("A_log"), (h,), kind="vector", init=("log_uniform", 1.0, 16.0)),
+            ParamSpec(t("D"), (h,), kind="vector", init=("ones",)),
+            ParamSpec(t("dt_bias"), (h,), kind="vector", init=("inv_softplus_log_uniform", 1e-3, 0.1)),
+            ParamSpec(t("out_proj.weight"), (self.hidden_size, self.d_ssm)),
         ]
         if self.conv_bias:
-            specs.append(ParamSpec("conv1d.bias", (c,), kind="vector"))
+            specs.append(ParamSpec(t("conv1d.bias"), (c,), kind="vector"))
         if self.proj_bias:
-            specs.append(ParamSpec("in_proj.bias", (self.proj_dim,), kind="vector"))
-            specs.append(ParamSpec("out_proj.bias", (self.hidden_size,), kind="vector"))
+            specs.append(ParamSpec(t("in_proj.bias"), (self.proj_dim,), kind="vector"))
+            specs.append(ParamSpec(t("out_proj.bias"), (self.hidden_size,), kind="vector"))
         if self.gated_norm:
-            specs.append(ParamSpec("norm.weight", (self.d_ssm,), kind="vector", init=("ones",)))
+            specs.append(ParamSpec(t("norm.weight"), (self.d_ssm,), kind="vector", init=("ones",)))
         return specs
 
     def ignored_names(self) -> List[str]:
         """Tensors a checkpoint may carry for switched-off options; present or not, unused."""
         names = []
         if not self.conv_bias:
-            names.append("conv1d.bias")
+            names.append(self._t("conv1d.bias"))
         if not self.gated_norm:
-            names.append("norm.weight")
+            names.append(self._t("norm.weight"))
         return names
 
     def state_specs(self) -> List[StateSpec]:
@@ -104,6 +118,9 @@ class Mamba2Mixer(Mixer):
                 StateSpec.fixed("ssm", (self.n_heads, self.d_head, self.d_state), "float32")]
 
     def bind(self, params: Dict[str, Tensor]) -> None:
+        if self.tensor_names:
+            back = {v: k for k, v in self.tensor_names.items()}
+            params = {back.get(k, k): v for k, v in params.items()}
         self.w_in = params["in_proj.weight"].contiguous()
         self.w_out = params["out_proj.weight"].contiguous()
         self.conv_w = params["conv1d.weight"].reshape(self.conv_dim, self.d_conv).contiguous()
@@ -233,7 +250,7 @@ class Mamba2Mixer(Mixer):
         if gate is not None:
             return y
         gated = ws.alloc((T, i_dim), proj.dtype)
-        K.gated_norm(y, z, self.z_scale, self.z_bias, self.norm_w, self.norm_eps, self.n_groups,
+        K.gated_norm(y, z, self.z_scale, self.z_bias, self.norm_w, self.norm_eps, self.norm_groups,
                      self.norm_before_gate, gated)
         return gated
 

@@ -1,0 +1,110 @@
+"""Routed feed-forward: a mixture of small gated experts, optionally beside a shared one.
+
+    z = Wr x + br (float arithmetic); a token's ``top`` experts are those with the largest z, their
+    weights p the softmax over the chosen z only;
+    expert e:  g = min(Wg_e x, limit), u = clamp(Wu_e x, -limit, limit),
+               y_e = Wd_e [ g * sigmoid(act_alpha * g) * (u + act_shift) ];
+    out = sum over the chosen e of p_e y_e  (+ the shared expert's output, same form with its own
+    width and limit, for every token).
+
+Tensors: ``router`` [E, D], ``router.b`` [E], ``e<i>.gate`` / ``e<i>.up`` [F, D], ``e<i>.down`` [D, F],
+``shared.gate`` / ``shared.up`` [Fs, D], ``shared.down`` [D, Fs].  The experts' matrices are stacked
+when they are bound ([E, 2F, D] with every expert's gate rows before its up rows, and [E, D, F]), so
+that the routed part of a step is a fixed chain of launches whatever the router decides: route, plan
+(the (token, choice) pairs sorted by expert, on the device), the grouped [gate | up] product with the
+activation in its epilogue, the grouped down product, and the weighted sum, which also adds the
+shared expert.  The router's weights and logits, the softmax and the weighted sum are float in both
+storage types.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kernels import ops as K
+from . import streaming
+from .base import FeedForward, ParamSpec, register_feed_forward
+
+Tensor = torch.Tensor
+
+
+class RoutedGLU(FeedForward):
+    def __init__(self, hidden_size: int, experts: int, top: int, expert_ff: int, expert_limit: float,
+                 shared_ff: int = 0, shared_limit: float = 0.0, act_alpha: float = 1.702, act_shift: float = 1.0,
+                 router_bias: bool = True, out_multiplier: float = 1.0):
+        if not 1 <= top <= experts:
+            raise ValueError("top must be between 1 and the number of experts")
+        if expert_ff <= 0 or shared_ff < 0:
+            raise ValueError("expert widths must be positive")
+        self.hidden_size = int(hidden_size)
+        self.experts, self.top, self.expert_ff = int(experts), int(top), int(expert_ff)
+        self.expert_limit, self.shared_ff, self.shared_limit = float(expert_limit), int(shared_ff), float(shared_limit)
+        self.act_alpha, self.act_shift = float(act_alpha), float(act_shift)
+        self.router_bias = bool(router_bias)
+        self.out_scale = float(out_multiplier)
+
+    def param_specs(self) -> List[ParamSpec]:
+        D, F = self.hidden_size, self.expert_ff
+        specs = [ParamSpec("router", (self.experts, D), kind="vector", init=("normal", 0.5))]
+        if self.router_bias:
+            specs.append(ParamSpec("router.b", (self.experts,), kind="vector", init=("normal", 0.5)))
+        for e in range(self.experts):
+            specs += [ParamSpec(f"e{e}.gate", (F, D), init=("normal", 0.1)), ParamSpec(f"e{e}.up", (F, D), init=("normal", 0.1)),
+                      ParamSpec(f"e{e}.down", (D, F), init=("normal", 0.1))]
+        if self.shared_ff > 0:
+            Fs = self.shared_ff
+            specs += [ParamSpec("shared.gate", (Fs, D), init=("normal", 0.1)), ParamSpec("shared.up", (Fs, D), init=("normal", 0.1)),
+                      ParamSpec("shared.down", (D, Fs), init=("normal", 0.1))]
+        return specs
+
+    def bind(self, params: Dict[str, Tensor]) -> None:
+        E = self.experts
+        self.router_w = params["router"].contiguous()
+        self.router_b = params["router.b"].contiguous() if self.router_bias else None
+        self.gate_up = torch.stack([torch.cat([params[f"e{e}.gate"], params[f"e{e}.up"]], dim=0) for e in range(E)]).contiguous()
+        self.down = torch.stack([params[f"e{e}.down"] for e in range(E)]).contiguous()
+        self.shared_gate_up: Optional[Tensor] = None
+        self.shared_down: Optional[Tensor] = None
+        if self.shared_ff > 0:
+            self.shared_gate_up = torch.cat([params["shared.gate"], params["shared.up"]], dim=0).contiguous()
+            self.shared_down = params["shared.down"].contiguous()
+
+    def _shared(self, x: Tensor, ctx) -> Tensor:
+        ws = ctx.workspace
+        T, Fs = x.shape[0], self.shared_ff
+        gu = ws.alloc((T, 2 * Fs), x.dtype)
+        streaming.linear(x, self.shared_gate_up, gu, ctx)
+        act = ws.alloc((T, Fs), x.dtype)
+        K.clamped_glu(gu, self.shared_limit, self.act_alpha, self.act_shift, act)
+        y = ws.alloc((T, self.hidden_size), x.dtype)
+        streaming.linear(act, self.shared_down, y, ctx)
+        return y
+
+    def forward(self, x: Tensor, ctx, out: Tensor) -> None:
+        ws = ctx.workspace
+        T, D = x.shape
+        E, top, F = self.experts, self.top, self.expert_ff
+        A = T * top
+        ids = ws.alloc((T, top), torch.int32)
+        weights = ws.alloc((T, top), torch.float32)
+        K.moe_route(x, self.router_w, self.router_b, top, ids, weights)
+        offsets = ws.alloc((E + 1,), torch.int32)
+        tile_start = ws.alloc((E + 1,), torch.int32)
+        perm = ws.alloc((A,), torch.int32)
+        # the tensor cores take bfloat16 rows whose length is a multiple of 8; anything else runs in float
+        act = ws.alloc((A, F), x.dtype)
+        tc = K.moe_gemm_tc_ok(x, self.gate_up) and K.moe_gemm_tc_ok(act, self.down)
+        K.moe_plan(ids, E, tc, offsets, tile_start, perm)
+        K.moe_gemm(x, self.gate_up, perm, offsets, tile_start, top, True, act, tc, limit=self.expert_limit,
+                   alpha=self.act_alpha, shift=self.act_shift)
+        y = ws.alloc((A, D), torch.float32)
+        K.moe_gemm(act, self.down, perm, offsets, tile_start, top, False, y, tc)
+        shared = self._shared(x, ctx) if self.shared_ff > 0 else None
+        K.moe_combine(y, weights, shared, out)
+
+    def streamed_weights(self) -> List[Tensor]:
+        return [w for w in (self.shared_gate_up, self.shared_down) if w is not None]
+
+
+register_feed_forward("routed_glu", RoutedGLU)

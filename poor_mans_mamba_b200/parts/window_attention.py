@@ -31,7 +31,56 @@ Tensor = torch.Tensor
 _TC_FROM_TOKENS = 256   # shorter steps stay on the mma.sync kernel (few 128-row tiles)
 
 
-class WindowSinkAttention(_StackedInput):
+class PagedSoftmaxAttention(_StackedInput):
+    """What the softmax-attention mixers over padded heads share: the tickets of the key splits and the
+    choice of the attention kernel for a step (`_attend`).  A subclass sets ``heads``, ``kv_heads``,
+    ``padded_dim``, ``window``, ``scale`` and, where it has one, ``sink``."""
+    sink: Optional[Tensor] = None
+
+    def _make_split_counter(self, device: torch.device) -> None:
+        # tickets of the key splits (zero between steps): the last block of a tile merges them
+        self._split_counter = torch.zeros(4096, dtype=torch.int32, device=device) if device.type == "cuda" else None
+        if self._split_counter is not None:
+            K.watch_split_counter(self._split_counter)  # cleared if a launch is ever abandoned half-way
+
+    def _attend(self, q_rot: Tensor, kv, ctx, attn: Tensor) -> None:
+        """The step's attention over the pages, which hold the step's keys and values already.  bfloat16
+        runs on the tensor cores where the padded head size is one the kernels take (decode steps: TMA
+        tiles or cp.async gathers; prompt steps of 256 tokens or more: tcgen05; shorter ones:
+        mma.sync); float32, and any other head size, on the float kernel."""
+        T, H, G, Dp, ws = q_rot.shape[0], self.heads, self.kv_heads, self.padded_dim, ctx.workspace
+        counter = self._split_counter
+        # (the tensor-core kernels take the row maximum before the scale is applied: positive scales only)
+        bf16 = q_rot.dtype == torch.bfloat16 and counter is not None and self.scale > 0.0
+
+        def scratch_for(n_splits):
+            return ws.alloc((K.attention_scratch_floats(T, H, Dp, n_splits),), torch.float32) if n_splits > 1 else None
+
+        if bf16 and ctx.decode_only and K.flash_decode_supported(H, G, Dp):
+            n_splits, split_len = plan_key_splits(H, G, Dp, self.window, ctx.new_lens, ctx.kv_len_bound, q_rot.dtype)
+            if n_splits <= 64 and counter.numel() >= T * G:
+                K.flash_decode_attention(q_rot, None, None, 1.0, 1.0, 1.0, None, kv.pool, kv.block_table, ctx.positions,
+                                         attn, H, G, Dp, self.scale, window=self.window, n_splits=n_splits,
+                                         split_len=split_len, scratch=scratch_for(n_splits), split_counter=counter,
+                                         sink=self.sink)
+                return
+        if (bf16 and not ctx.decode_only and sum(ctx.new_lens) >= _TC_FROM_TOKENS
+                and K.attention_tc_supported(H, G, Dp, kv.pool.shape[2])):
+            n_splits, split_len = plan_key_splits_tc(H, G, self.window, ctx.new_lens, ctx.kv_len_bound)
+            per_tile = 128 // (H // G)
+            tiles = sum((n + per_tile - 1) // per_tile for n in ctx.new_lens)
+            if n_splits <= 64 and counter.numel() >= tiles * G:
+                K.attention_tc(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.cu_seqlens, ctx.new_lens, attn, H, G, Dp,
+                               self.scale, window=self.window, n_splits=n_splits, split_len=split_len,
+                               scratch=scratch_for(n_splits), split_counter=counter, sink=self.sink)
+                return
+        n_splits, split_len = plan_key_splits(H, G, Dp, self.window, ctx.new_lens, ctx.kv_len_bound, q_rot.dtype)
+        K.paged_attention(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.seq_of, attn, H, G, Dp, self.scale,
+                          window=self.window, n_splits=n_splits, split_len=split_len, scratch=scratch_for(n_splits),
+                          cu_seqlens=ctx.cu_seqlens, new_lens=ctx.new_lens, split_counter=counter, sink=self.sink)
+
+
+class WindowSinkAttention(PagedSoftmaxAttention):
     def __init__(self, hidden_size: int, heads: int, kv_heads: int, dim: int, vdim: int, conv: int, window: int,
                  rot_dims: int, rot_base: float, scale: float):
         if heads % kv_heads:
@@ -85,10 +134,7 @@ class WindowSinkAttention(_StackedInput):
             i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
             inv = torch.pow(torch.tensor(self.rot_base, dtype=torch.float64), -2.0 * i / float(self.rot_dims))
             self.inv_freq = inv.to(device=device, dtype=torch.float32).contiguous()
-        # tickets of the key splits (zero between steps): the last block of a tile merges them
-        self._split_counter = torch.zeros(4096, dtype=torch.int32, device=device) if device.type == "cuda" else None
-        if self._split_counter is not None:
-            K.watch_split_counter(self._split_counter)  # cleared if a launch is ever abandoned half-way
+        self._make_split_counter(device)
 
     def forward_projected(self, proj: Tensor, ctx, cache, out: Tensor) -> None:
         T = proj.shape[0]
@@ -110,43 +156,6 @@ class WindowSinkAttention(_StackedInput):
 
     def output_bias(self) -> Optional[Tensor]:
         return self.out_bias
-
-
-    def _attend(self, q_rot: Tensor, kv, ctx, attn: Tensor) -> None:
-        """The step's attention over the pages, which hold the step's keys and values already.  bfloat16
-        runs on the tensor cores where the padded head size is one the kernels take (decode steps: TMA
-        tiles or cp.async gathers; prompt steps of 256 tokens or more: tcgen05; shorter ones:
-        mma.sync); float32, and any other head size, on the float kernel."""
-        T, H, G, Dp, ws = q_rot.shape[0], self.heads, self.kv_heads, self.padded_dim, ctx.workspace
-        counter = self._split_counter
-        # (the tensor-core kernels take the row maximum before the scale is applied: positive scales only)
-        bf16 = q_rot.dtype == torch.bfloat16 and counter is not None and self.scale > 0.0
-
-        def scratch_for(n_splits):
-            return ws.alloc((K.attention_scratch_floats(T, H, Dp, n_splits),), torch.float32) if n_splits > 1 else None
-
-        if bf16 and ctx.decode_only and K.flash_decode_supported(H, G, Dp):
-            n_splits, split_len = plan_key_splits(H, G, Dp, self.window, ctx.new_lens, ctx.kv_len_bound, q_rot.dtype)
-            if n_splits <= 64 and counter.numel() >= T * G:
-                K.flash_decode_attention(q_rot, None, None, 1.0, 1.0, 1.0, None, kv.pool, kv.block_table, ctx.positions,
-                                         attn, H, G, Dp, self.scale, window=self.window, n_splits=n_splits,
-                                         split_len=split_len, scratch=scratch_for(n_splits), split_counter=counter,
-                                         sink=self.sink)
-                return
-        if (bf16 and not ctx.decode_only and sum(ctx.new_lens) >= _TC_FROM_TOKENS
-                and K.attention_tc_supported(H, G, Dp, kv.pool.shape[2])):
-            n_splits, split_len = plan_key_splits_tc(H, G, self.window, ctx.new_lens, ctx.kv_len_bound)
-            per_tile = 128 // (H // G)
-            tiles = sum((n + per_tile - 1) // per_tile for n in ctx.new_lens)
-            if n_splits <= 64 and counter.numel() >= tiles * G:
-                K.attention_tc(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.cu_seqlens, ctx.new_lens, attn, H, G, Dp,
-                               self.scale, window=self.window, n_splits=n_splits, split_len=split_len,
-                               scratch=scratch_for(n_splits), split_counter=counter, sink=self.sink)
-                return
-        n_splits, split_len = plan_key_splits(H, G, Dp, self.window, ctx.new_lens, ctx.kv_len_bound, q_rot.dtype)
-        K.paged_attention(q_rot, kv.pool, kv.block_table, ctx.positions, ctx.seq_of, attn, H, G, Dp, self.scale,
-                          window=self.window, n_splits=n_splits, split_len=split_len, scratch=scratch_for(n_splits),
-                          cu_seqlens=ctx.cu_seqlens, new_lens=ctx.new_lens, split_counter=counter, sink=self.sink)
 
 
 register_mixer("window_sink_attention", WindowSinkAttention)
