@@ -20,9 +20,10 @@ Peaks come from MEASURED_PEAKS.json beside this file when present, else from the
 fallback.  Inputs of a decode step (1 GB of weights plus the caches) exceed the L2, so no
 L2 flush is needed between timed iterations.
 
-`--workload compare` is a measurement beside the benchmark (its own JSON line): a Boketar model and a
-Falcon-H1 model of equal width, feed-forward size, layer count and vocabulary, one prompt step and
-decode steps of each with the L2 flushed before every timed step, and every kernel's device time.
+`--workload compare` is a measurement beside the benchmark (its own JSON line): a Boketar model (or, with
+`--design tafesun`, a Tafesun model) and a Falcon-H1 model of equal width, feed-forward size, layer count and
+vocabulary, one prompt step and decode steps of each with the L2 flushed before every timed step, and every
+kernel's device time.
 """
 from __future__ import annotations
 
@@ -492,6 +493,34 @@ def boketar_config(width, ff, vocab, sizes, layers):
             "norm": {"eps": 1e-6}, "layers": out}
 
 
+# `--workload compare --design tafesun`: a Tafesun model beside the Falcon-H1 model.  Its attention and its
+# state-space mixer have Falcon-H1's sizes; its routed feed-forward reads as many weights a token as the dense
+# one (top * expert ff + shared ff = ff).  name -> (experts, top, expert ff, shared ff).
+TAFESUN_FF = {"0.5b": (16, 4, 256, 1024), "7b": (32, 4, 2048, 4096)}
+
+
+def tafesun_config(falcon, ff_sizes, layers):
+    """`layers` parallel layers, every one with a routed feed-forward; the second half uses the tensors of
+    the first half where there are at least four layers."""
+    experts, top, expert_ff, shared_ff = ff_sizes
+    hd = falcon["head_dim"]
+    left = {"heads": falcon["num_attention_heads"], "kv_heads": falcon["num_key_value_heads"], "dim": hd, "vdim": hd,
+            "scale": hd ** -0.5, "rot": {"dims": hd // 2, "base": 1e6, "scaling": {"factor": 4.0}}}
+    right = {"heads": falcon["mamba_n_heads"], "vdim": falcon["mamba_d_head"], "state": falcon["mamba_d_state"],
+             "groups": falcon["mamba_n_groups"], "conv": falcon["mamba_d_conv"], "norm_groups": falcon["mamba_n_groups"]}
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff, "limit": 7.0},
+           "shared": {"ff": shared_ff, "limit": 7.0}}
+    out = []
+    for i in range(layers):
+        layer = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0},
+                 "mlp": mlp}
+        if layers >= 4 and i >= layers // 2 and i - layers // 2 < layers // 2:
+            layer["weights_of"] = i - layers // 2
+        out.append(layer)
+    return {"architecture": "Tafesun", "vocab": falcon["vocab_size"], "width": falcon["hidden_size"],
+            "norm": {"eps": 1e-6}, "logit_scale": 1.0, "layers": out}
+
+
 def compare_workload(args, peaks) -> int:
     import torch
 
@@ -506,7 +535,12 @@ def compare_workload(args, peaks) -> int:
     falcon.update(falcon_keys)
     falcon["num_hidden_layers"] = layers
     vocab = falcon["vocab_size"]
-    configs = {"boketar": boketar_config(width, ff, vocab, bk_sizes, layers), "falcon_h1": falcon}
+    if args.design == "tafesun":
+        configs = {"tafesun": tafesun_config(falcon, TAFESUN_FF[args.sizes], layers), "falcon_h1": falcon}
+        design_sizes = {"tafesun_ff": dict(zip(("experts", "top", "expert_ff", "shared_ff"), TAFESUN_FF[args.sizes]))}
+    else:
+        configs = {"boketar": boketar_config(width, ff, vocab, bk_sizes, layers), "falcon_h1": falcon}
+        design_sizes = {"boketar_sizes": bk_sizes}
     prompt, batch, ctx_len = args.prompt_tokens, args.batch, args.context
     rng = random.Random(3)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")  # larger than the L2
@@ -595,7 +629,7 @@ def compare_workload(args, peaks) -> int:
     print(json.dumps({"workload": "compare", "sizes": args.sizes, "layers": layers, "width": width, "ff": ff,
                       "vocab": vocab, "dtype": args.dtype, "data": "synthetic", "prompt_tokens": prompt,
                       "decode_batch": batch, "decode_context": ctx_len, "l2": "flushed before every timed step",
-                      "boketar_sizes": bk_sizes, "clocks": clocks.summary(), "peaks": peaks, **result}))
+                      **design_sizes, "clocks": clocks.summary(), "peaks": peaks, **result}))
     return 0
 
 
@@ -625,6 +659,8 @@ def main() -> int:
                          "count (--layers, default 4) and vocabulary at --sizes 0.5b or 7b: one prompt step of "
                          "--prompt-tokens and decode steps of --batch requests at --context, device-timed with the "
                          "L2 flushed, and the device time of every kernel of one step of each")
+    ap.add_argument("--design", default="boketar", choices=["boketar", "tafesun"],
+                    help="--workload compare: the model that is measured beside Falcon-H1")
     ap.add_argument("--no-check", dest="check", action="store_false",
                     help="skip the comparison with the plain implementation that runs before the timing: the first "
                          "two layers of the run's model, in the run's dtype, on the benchmark's schedule (a "

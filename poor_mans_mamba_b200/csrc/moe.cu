@@ -142,6 +142,47 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The whole plan of a step with few pairs (a decode step) in one block and one launch: a thread per expert
+// counts its pairs, one thread sums, then every expert's thread writes its pairs in their order.
+constexpr int kPlanSmallPairs = 512;
+
+__global__ void __launch_bounds__(256)
+    moe_plan_small_kernel(const int* __restrict__ ids, int A, int E, int tile_rows, int* __restrict__ offsets,
+                          int* __restrict__ tile_start, int* __restrict__ perm) {
+  extern __shared__ int plan_small[];  // ids [A] | counts, then starts [E]
+  int* ids_s = plan_small;
+  int* cnt = plan_small + A;
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int i = threadIdx.x; i < A; i += blockDim.x) ids_s[i] = ids[i];
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int c = 0;
+    for (int i = 0; i < A; ++i) c += ids_s[i] == e;
+    cnt[e] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int rows = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = cnt[e];
+      offsets[e] = rows;
+      tile_start[e] = tiles;
+      cnt[e] = rows;
+      rows += c;
+      tiles += (c + tile_rows - 1) / tile_rows;
+    }
+    offsets[E] = rows;
+    tile_start[E] = tiles;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int pos = cnt[e];
+    for (int i = 0; i < A; ++i)
+      if (ids_s[i] == e) perm[pos++] = i;
+  }
+}
+
 __device__ __forceinline__ float clamped_glu(float g, float u, float limit, float alpha, float shift) {
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
@@ -381,11 +422,17 @@ PMM_EXPORT int pmm_moe_route(const void* x, long long ld_x, const float* w, cons
   return pmm::launch_status();
 }
 
-// ids [A] -> offsets [E + 1], tile_start [E + 1] (row tiles of `tile_rows`), perm [A].  Two launches.
+// ids [A] -> offsets [E + 1], tile_start [E + 1] (row tiles of `tile_rows`), perm [A].  One launch for up to
+// kPlanSmallPairs pairs, else two.
 PMM_EXPORT int pmm_moe_plan(const int* ids, int A, int E, int tile_rows, int* offsets, int* tile_start, int* perm,
                             cudaStream_t stream) {
   if (A <= 0) return 0;
   if (E <= 0 || E > 4096 || tile_rows <= 0) return PMM_ERR_BAD_ARGUMENT;
+  if (A <= pmm::kPlanSmallPairs) {
+    pmm::launch_pdl(pmm::moe_plan_small_kernel, dim3(1), dim3(256), static_cast<size_t>(A + E) * sizeof(int), stream, ids,
+                    A, E, tile_rows, offsets, tile_start, perm);
+    return pmm::launch_status();
+  }
   pmm::launch_pdl(pmm::moe_plan_kernel, dim3(1), dim3(1024), static_cast<size_t>(E) * sizeof(int), stream, ids, A, E,
                   tile_rows, offsets, tile_start);
   int rc = pmm::launch_status();

@@ -40,7 +40,10 @@ constexpr int kTcABytes = kTcM * kTcK * 2;  // 32 KB
 constexpr int kTcBBytes = kTcN * kTcK * 2;  // 32 KB
 constexpr size_t kTcSmem = static_cast<size_t>(kTcStages) * (kTcABytes + kTcBBytes) + 1024 /*alignment*/;
 
-enum { kTcPlain = 0, kTcSwiglu = 1 };
+// kTcClampedGlu: the gate and up layout of kTcSwiglu with the activation
+//   g = min(gate, limit); u = clamp(up, -limit, limit); act = g * sigmoid(alpha * g) * (u + shift)
+// (limit rides in gate_mult's place).
+enum { kTcPlain = 0, kTcSwiglu = 1, kTcClampedGlu = 2 };
 
 // kind::f16 instruction descriptor: float accumulate, bfloat16 A and B, both K-major, N, M.
 constexpr unsigned kTcIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kTcN >> 3) << 17) | ((kTcMH >> 4) << 24);
@@ -48,8 +51,8 @@ constexpr unsigned kTcIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kTcN >> 3) 
 template <int MODE>
 __global__ void __launch_bounds__(kTcThreads)
     tc_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                   bf16* __restrict__ out, long long ld_out, int T, int K, int F, float gate_mult,
-                   int* __restrict__ status) {
+                   bf16* __restrict__ out, long long ld_out, int T, int K, int F, float gate_mult, float act_alpha,
+                   float act_shift, int* __restrict__ status) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ unsigned char smem_raw[];
@@ -64,7 +67,7 @@ __global__ void __launch_bounds__(kTcThreads)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * kTcM;
-  const int n0 = blockIdx.y * (MODE == kTcSwiglu ? kTcN / 2 : kTcN);  // first output column
+  const int n0 = blockIdx.y * (MODE != kTcPlain ? kTcN / 2 : kTcN);  // first output column
   const int k_blocks = K / kTcK;
 
   if (threadIdx.x == 0) {
@@ -101,7 +104,7 @@ __global__ void __launch_bounds__(kTcThreads)
         mbar_expect_tx(&bar_full[s], kTcABytes + kTcBBytes);
         tma_load_2d(sA + s * kTcABytes, &map_x, kb * kTcK, m0, &bar_full[s]);                               // tokens 0..127
         tma_load_2d(sA + s * kTcABytes + kTcABytes / 2, &map_x, kb * kTcK, m0 + kTcMH, &bar_full[s]);      // tokens 128..255
-        if (MODE == kTcSwiglu) {
+        if (MODE != kTcPlain) {
           tma_load_2d(sB + s * kTcBBytes, &map_w, kb * kTcK, n0, &bar_full[s]);                      // gate rows
           tma_load_2d(sB + s * kTcBBytes + kTcBBytes / 2, &map_w, kb * kTcK, F + n0, &bar_full[s]);  // up rows
         } else {
@@ -159,7 +162,7 @@ __global__ void __launch_bounds__(kTcThreads)
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const int m = m0 + mhalf * kTcMH + quad * 32 + lane;  // this thread's token row
       const unsigned lane_base = tmem_base + (static_cast<unsigned>(quad * 32) << 16) + mhalf * kTcN;
-      if (MODE == kTcSwiglu) {
+      if (MODE != kTcPlain) {
 #pragma unroll 1
         for (int c = 0; c < kTcN / 64; ++c) {
           unsigned g[32], u[32];
@@ -174,9 +177,17 @@ __global__ void __launch_bounds__(kTcThreads)
               __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pack);
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const float g0 = __uint_as_float(g[j + 2 * e]) * gate_mult, g1 = __uint_as_float(g[j + 2 * e + 1]) * gate_mult;
-                p2[e] = __floats2bfloat162_rn(silu_fast(g0) * __uint_as_float(u[j + 2 * e]),
-                                              silu_fast(g1) * __uint_as_float(u[j + 2 * e + 1]));
+                if (MODE == kTcClampedGlu) {
+                  const float g0 = fminf(__uint_as_float(g[j + 2 * e]), gate_mult), g1 = fminf(__uint_as_float(g[j + 2 * e + 1]), gate_mult);
+                  const float u0 = fminf(fmaxf(__uint_as_float(u[j + 2 * e]), -gate_mult), gate_mult);
+                  const float u1 = fminf(fmaxf(__uint_as_float(u[j + 2 * e + 1]), -gate_mult), gate_mult);
+                  p2[e] = __floats2bfloat162_rn(__fdividef(g0, 1.f + __expf(-act_alpha * g0)) * (u0 + act_shift),
+                                                __fdividef(g1, 1.f + __expf(-act_alpha * g1)) * (u1 + act_shift));
+                } else {
+                  const float g0 = __uint_as_float(g[j + 2 * e]) * gate_mult, g1 = __uint_as_float(g[j + 2 * e + 1]) * gate_mult;
+                  p2[e] = __floats2bfloat162_rn(silu_fast(g0) * __uint_as_float(u[j + 2 * e]),
+                                                silu_fast(g1) * __uint_as_float(u[j + 2 * e + 1]));
+                }
               }
               *reinterpret_cast<uint4*>(dst + j) = pack;
             }
@@ -232,36 +243,50 @@ inline bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
 // multiple of 128 (SwiGLU: F) or 256 (plain), 16-byte aligned rows.
 PMM_EXPORT int pmm_tc_gemm_supported(int mode, int K, int n_out, long long ldx, long long ld_out) {
   if (K <= 0 || K % pmm::kTcK || ldx % 8 || ld_out % 8) return 0;
-  return mode == pmm::kTcSwiglu ? (n_out % 128 == 0) : (n_out % 256 == 0);
+  return mode != pmm::kTcPlain ? (n_out % 128 == 0) : (n_out % 256 == 0);
 }
 
 // mode 1: out[T, F] = silu((x Wg^T) * gate_mult) * (x Wu^T) with w = [Wg; Wu] ([2F, K]).
+// mode 2: the same layout with the clamped gated activation (limit = gate_mult, act_alpha, act_shift).
 // mode 0: out[T, N] = x w^T with w [N, K].  status: one int, stays 0 unless a bounded wait gave up.
-PMM_EXPORT int pmm_tc_gemm(int mode, const void* x, long long ldx, const void* w, void* out, long long ld_out, int T,
-                           int K, int n_out, float gate_mult, int* status, cudaStream_t stream) {
+namespace pmm {
+template <int MODE>
+int launch_tc_gemm(const CUtensorMap& map_x, const CUtensorMap& map_w, dim3 grid, void* out, long long ld_out, int T, int K,
+                   int n_out, float gate_mult, float act_alpha, float act_shift, int* status, cudaStream_t stream) {
+  auto kern = tc_gemm_kernel<MODE>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kTcSmem));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  launch_pdl(kern, grid, dim3(kTcThreads), kTcSmem, stream, map_x, map_w, static_cast<bf16*>(out), ld_out, T, K, n_out,
+             gate_mult, act_alpha, act_shift, status);
+  return launch_status();
+}
+}  // namespace pmm
+
+PMM_EXPORT int pmm_tc_gemm_act(int mode, const void* x, long long ldx, const void* w, void* out, long long ld_out, int T,
+                               int K, int n_out, float gate_mult, float act_alpha, float act_shift, int* status,
+                               cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (!pmm_tc_gemm_supported(mode, K, n_out, ldx, ld_out) || !status) return PMM_ERR_BAD_ARGUMENT;
+  if (mode < 0 || mode > 2 || !pmm_tc_gemm_supported(mode, K, n_out, ldx, ld_out) || !status) return PMM_ERR_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(w) % 16 || reinterpret_cast<uintptr_t>(out) % 16)
     return PMM_ERR_BAD_ARGUMENT;
   CUtensorMap map_x, map_w;
-  const long long w_rows = mode == pmm::kTcSwiglu ? 2LL * n_out : n_out;
+  const long long w_rows = mode != pmm::kTcPlain ? 2LL * n_out : n_out;
   if (!pmm::make_map(&map_x, x, T, K, ldx, pmm::kTcMH) || !pmm::make_map(&map_w, w, w_rows, K, K, pmm::kTcN / 2))
     return PMM_ERR_BAD_ARGUMENT;
-  const int cols_per_block = mode == pmm::kTcSwiglu ? pmm::kTcN / 2 : pmm::kTcN;
+  const int cols_per_block = mode != pmm::kTcPlain ? pmm::kTcN / 2 : pmm::kTcN;
   dim3 grid((T + pmm::kTcM - 1) / pmm::kTcM, n_out / cols_per_block);
-  cudaError_t e;
-  if (mode == pmm::kTcSwiglu) {
-    auto kern = pmm::tc_gemm_kernel<pmm::kTcSwiglu>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pmm::kTcSmem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    pmm::launch_pdl(kern, grid, dim3(pmm::kTcThreads), pmm::kTcSmem, stream, map_x, map_w, static_cast<pmm::bf16*>(out), ld_out, T,
-                    K, n_out, gate_mult, status);
-  } else {
-    auto kern = pmm::tc_gemm_kernel<pmm::kTcPlain>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pmm::kTcSmem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    pmm::launch_pdl(kern, grid, dim3(pmm::kTcThreads), pmm::kTcSmem, stream, map_x, map_w, static_cast<pmm::bf16*>(out), ld_out, T,
-                    K, n_out, gate_mult, status);
-  }
-  return pmm::launch_status();
+  if (mode == pmm::kTcSwiglu)
+    return pmm::launch_tc_gemm<pmm::kTcSwiglu>(map_x, map_w, grid, out, ld_out, T, K, n_out, gate_mult, act_alpha, act_shift,
+                                               status, stream);
+  if (mode == pmm::kTcClampedGlu)
+    return pmm::launch_tc_gemm<pmm::kTcClampedGlu>(map_x, map_w, grid, out, ld_out, T, K, n_out, gate_mult, act_alpha,
+                                                   act_shift, status, stream);
+  return pmm::launch_tc_gemm<pmm::kTcPlain>(map_x, map_w, grid, out, ld_out, T, K, n_out, gate_mult, act_alpha, act_shift,
+                                            status, stream);
+}
+
+PMM_EXPORT int pmm_tc_gemm(int mode, const void* x, long long ldx, const void* w, void* out, long long ld_out, int T,
+                           int K, int n_out, float gate_mult, int* status, cudaStream_t stream) {
+  if (mode != pmm::kTcPlain && mode != pmm::kTcSwiglu) return PMM_ERR_BAD_ARGUMENT;
+  return pmm_tc_gemm_act(mode, x, ldx, w, out, ld_out, T, K, n_out, gate_mult, 0.f, 0.f, status, stream);
 }

@@ -109,6 +109,8 @@ _SIGNATURES = {
     "pmm_tc_gemm_supported": [c_int, c_int, c_int, c_longlong, c_longlong],
     "pmm_tc_gemm": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_float,
                     c_void_p, c_void_p],
+    "pmm_tc_gemm_act": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_float,
+                        c_float, c_float, c_void_p, c_void_p],
     "pmm_silu_mul": [c_void_p, c_longlong, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_add_row_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "pmm_add_tanh_norm": [c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -123,6 +125,11 @@ _SIGNATURES = {
     "pmm_moe_gemm": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                      c_int, c_float, c_float, c_float, c_void_p, c_int, c_int, c_void_p],
     "pmm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "pmm_moe_tc_tile_rows": [],
+    "pmm_moe_tc_supported": [c_int, c_int, c_longlong],
+    "pmm_moe_gather_rows": [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
+    "pmm_moe_tc_gemm": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                        c_float, c_float, c_float, c_void_p, c_void_p, c_void_p],
     "pmm_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                         c_void_p, c_void_p, c_void_p],
 }
@@ -1319,6 +1326,19 @@ def tc_gemm_swiglu(x: Tensor, gate_up: Tensor, gate_mult: float, out: Tensor) ->
           float(gate_mult), _tc_status(x.device).data_ptr(), _stream())
 
 
+def tc_gemm_clamped_glu(x: Tensor, gate_up: Tensor, limit: float, alpha: float, shift: float, out: Tensor) -> None:
+    """out[T, F] = g * sigmoid(alpha g) * (u + shift), g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit), with
+    gate_up = [Wg; Wu] ([2F, K]): one tcgen05 launch, the activation in its epilogue."""
+    _cuda(x, gate_up, out)
+    T, Kd = x.shape
+    F = out.shape[1]
+    if not (gate_up.shape == (2 * F, Kd) and out.shape[0] == T and tc_gemm_supported(x, gate_up, F, True)
+            and out.dtype == torch.bfloat16 and out.stride(1) == 1):
+        raise KernelError("tc_gemm_clamped_glu: sizes or alignment outside what the kernel takes")
+    _call("pmm_tc_gemm_act", 2, x.data_ptr(), x.stride(0), gate_up.data_ptr(), out.data_ptr(), out.stride(0), T, Kd, F,
+          float(limit), float(alpha), float(shift), _tc_status(x.device).data_ptr(), _stream())
+
+
 def tc_gemm(x: Tensor, weight: Tensor, out: Tensor) -> None:
     """out[T, N] = x @ weight^T on tcgen05 (bfloat16 in and out, float accumulation)."""
     _cuda(x, weight, out)
@@ -1434,27 +1454,63 @@ def moe_route(x: Tensor, router_w: Tensor, router_b: Optional[Tensor], top: int,
           weights.data_ptr(), T, D, E, int(top), _dt(x), _stream())
 
 
-def moe_tile_rows(tensor_cores: bool) -> int:
-    return int(_fn("pmm_moe_tile_rows")(int(bool(tensor_cores))))
+def moe_tile_rows(form: str) -> int:
+    """Rows of a row tile of the grouped products: ``form`` "float" (CUDA cores, any sizes), "mma" (mma.sync) or
+    "tcgen05"."""
+    if form == "tcgen05":
+        return int(_fn("pmm_moe_tc_tile_rows")())
+    return int(_fn("pmm_moe_tile_rows")(int(form == "mma")))
 
 
-def moe_row_tiles(n_pairs: int, n_experts: int, tensor_cores: bool) -> int:
-    """Upper bound of the row tiles of a plan over ``n_pairs`` (token, choice) pairs."""
-    return n_pairs // moe_tile_rows(tensor_cores) + min(n_experts, n_pairs)
-
-
-def moe_plan(ids: Tensor, n_experts: int, tensor_cores: bool, offsets: Tensor, tile_start: Tensor, perm: Tensor) -> None:
-    """Sorts the pairs by expert: offsets, tile_start [E + 1] int32, perm [T * top] int32."""
+def moe_plan(ids: Tensor, n_experts: int, form: str, offsets: Tensor, tile_start: Tensor, perm: Tensor) -> None:
+    """Sorts the pairs by expert: offsets, tile_start [E + 1] int32 (row tiles of the given form of the grouped
+    products), perm [T * top] int32."""
     _cuda(ids, offsets, tile_start, perm)
     A = ids.numel()
     for t, n, what in ((offsets, n_experts + 1, "offsets"), (tile_start, n_experts + 1, "tile_start"), (perm, A, "perm")):
         if not (t.dtype == torch.int32 and t.is_contiguous() and t.numel() == n):
             raise KernelError(f"moe_plan: {what} must be contiguous int32 of {n}")
     _i32(ids, "moe_plan: ids")
-    _call("pmm_moe_plan", ids.data_ptr(), A, int(n_experts), moe_tile_rows(tensor_cores), offsets.data_ptr(),
+    _call("pmm_moe_plan", ids.data_ptr(), A, int(n_experts), moe_tile_rows(form), offsets.data_ptr(),
           tile_start.data_ptr(), perm.data_ptr(), _stream())
-    global launch_count
-    launch_count += 1  # two launches
+    if A > 512:
+        global launch_count
+        launch_count += 1  # two launches for many pairs
+
+
+def moe_tc_supported(a: Tensor, w: Tensor, n_out: int) -> bool:
+    """Whether the tcgen05 grouped product takes these operands (bfloat16, K a multiple of 64, N of 8)."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.stride(1) == 1 and a.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and bool(_fn("pmm_moe_tc_supported")(a.shape[1], int(n_out), a.stride(0))))
+
+
+def moe_gather_rows(x: Tensor, perm: Tensor, top: int, out: Tensor) -> None:
+    """out[i] = x[perm[i] // top]: the token rows in the order of the sorted pairs (bfloat16)."""
+    _cuda(x, perm, out)
+    A, Kd = out.shape
+    if not (x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.is_contiguous() and x.shape[1] == Kd
+            and perm.numel() == A and Kd % 8 == 0):
+        raise KernelError("moe_gather_rows: bfloat16 rows of a multiple of 8 elements, one output row per pair")
+    _call("pmm_moe_gather_rows", x.data_ptr(), _rows_view(x, "moe_gather_rows"), perm.data_ptr(), A, int(top),
+          out.data_ptr(), Kd, _stream())
+
+
+def moe_tc_gemm(a: Tensor, w: Tensor, perm: Tensor, offsets: Tensor, tile_start: Tensor, up: bool, out: Tensor,
+                limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0) -> None:
+    """The grouped product on the fifth-generation tensor cores.  a [pairs, K]: rows in the order of the sorted
+    pairs (the gathered token rows, or the activation); w [E, N (2N), K]; the plan made for "tcgen05" row tiles.
+    ``up``: out = act [pairs, N] bfloat16 with the clamped gated activation; else out = y [pairs, N] float32 in
+    the order of the pairs."""
+    _cuda(a, w, perm, offsets, tile_start, out)
+    A, Kd = a.shape
+    E, N = w.shape[0], out.shape[1]
+    if not (w.dim() == 3 and w.is_contiguous() and w.shape == (E, (2 if up else 1) * N, Kd) and perm.numel() == A
+            and out.shape == (A, N) and out.is_contiguous() and out.dtype == (torch.bfloat16 if up else torch.float32)
+            and offsets.numel() == E + 1 and tile_start.numel() == E + 1 and moe_tc_supported(a, w, N)):
+        raise KernelError("moe_tc_gemm: operands outside what the kernel takes")
+    _call("pmm_moe_tc_gemm", a.data_ptr(), a.stride(0), w.data_ptr(), perm.data_ptr(), offsets.data_ptr(),
+          tile_start.data_ptr(), A, E, Kd, N, int(bool(up)), float(limit), float(alpha), float(shift), out.data_ptr(),
+          _tc_status(a.device).data_ptr(), _stream())
 
 
 def moe_gemm_tc_ok(a: Tensor, w: Tensor) -> bool:

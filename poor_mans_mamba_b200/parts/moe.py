@@ -18,15 +18,23 @@ storage types.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
 
 from ..kernels import ops as K
-from . import streaming
+from . import branches, streaming
 from .base import FeedForward, ParamSpec, register_feed_forward
 
 Tensor = torch.Tensor
+
+# The grouped products of steps with at least this many (token, choice) pairs run on tcgen05
+# (PMM_TCGEN05_MOE=0: the mma.sync form throughout).
+_TC_FROM_PAIRS = 1024
+_TC_FROM_TILES = 96      # the shared expert's fused [gate | up] launch, as for the dense feed-forward
+_SIDE_SHARED = os.environ.get("PMM_SIDE_SHARED_EXPERT", "1") == "1"
+_TC_MOE = os.environ.get("PMM_TCGEN05_MOE", "1") == "1"
 
 
 class RoutedGLU(FeedForward):
@@ -70,16 +78,20 @@ class RoutedGLU(FeedForward):
             self.shared_gate_up = torch.cat([params["shared.gate"], params["shared.up"]], dim=0).contiguous()
             self.shared_down = params["shared.down"].contiguous()
 
-    def _shared(self, x: Tensor, ctx) -> Tensor:
+    def _shared(self, x: Tensor, y: Tensor, ctx) -> None:
+        """y = the shared expert's output for every token."""
         ws = ctx.workspace
         T, Fs = x.shape[0], self.shared_ff
-        gu = ws.alloc((T, 2 * Fs), x.dtype)
-        streaming.linear(x, self.shared_gate_up, gu, ctx)
         act = ws.alloc((T, Fs), x.dtype)
-        K.clamped_glu(gu, self.shared_limit, self.act_alpha, self.act_shift, act)
-        y = ws.alloc((T, self.hidden_size), x.dtype)
+        tiles = ((T + 255) // 256) * (Fs // 128)
+        if _TC_MOE and tiles >= _TC_FROM_TILES and K.tc_gemm_supported(x, self.shared_gate_up, Fs, True):
+            # prompt steps: [gate | up] with the activation in the epilogue of one tcgen05 launch
+            K.tc_gemm_clamped_glu(x, self.shared_gate_up, self.shared_limit, self.act_alpha, self.act_shift, act)
+        else:
+            gu = ws.alloc((T, 2 * Fs), x.dtype)
+            streaming.linear(x, self.shared_gate_up, gu, ctx)
+            K.clamped_glu(gu, self.shared_limit, self.act_alpha, self.act_shift, act)
         streaming.linear(act, self.shared_down, y, ctx)
-        return y
 
     def forward(self, x: Tensor, ctx, out: Tensor) -> None:
         ws = ctx.workspace
@@ -92,15 +104,40 @@ class RoutedGLU(FeedForward):
         offsets = ws.alloc((E + 1,), torch.int32)
         tile_start = ws.alloc((E + 1,), torch.int32)
         perm = ws.alloc((A,), torch.int32)
-        # the tensor cores take bfloat16 rows whose length is a multiple of 8; anything else runs in float
         act = ws.alloc((A, F), x.dtype)
-        tc = K.moe_gemm_tc_ok(x, self.gate_up) and K.moe_gemm_tc_ok(act, self.down)
-        K.moe_plan(ids, E, tc, offsets, tile_start, perm)
-        K.moe_gemm(x, self.gate_up, perm, offsets, tile_start, top, True, act, tc, limit=self.expert_limit,
-                   alpha=self.act_alpha, shift=self.act_shift)
         y = ws.alloc((A, D), torch.float32)
-        K.moe_gemm(act, self.down, perm, offsets, tile_start, top, False, y, tc)
-        shared = self._shared(x, ctx) if self.shared_ff > 0 else None
+        # The shared expert only shares the input with the routed ones: it runs on a side stream beside their
+        # chain of launches (a parallel branch of a recorded step) and is joined before the weighted sum.
+        shared = side = None
+        if self.shared_ff > 0:
+            shared = ws.alloc((T, D), x.dtype)
+            if x.is_cuda and _SIDE_SHARED:
+                main = torch.cuda.current_stream(x.device)
+                side = branches.branch_stream(x.device, "shared_expert")
+                with branches.fork(main, side):
+                    self._shared(x, shared, ctx)
+            else:
+                self._shared(x, shared, ctx)
+        # Steps of many tokens in bfloat16: tcgen05 tiles of 128 sorted rows (the token rows are gathered
+        # into that order first).  Fewer pairs, or rows that are no whole 128-byte pieces: mma.sync tiles of
+        # 64 rows, which read the token rows through the plan.  Anything else (float32, rows that are no
+        # multiple of 8 elements) runs in float on the CUDA cores.
+        if (_TC_MOE and A >= _TC_FROM_PAIRS and K.moe_tc_supported(x, self.gate_up, F)
+                and K.moe_tc_supported(act, self.down, D)):
+            K.moe_plan(ids, E, "tcgen05", offsets, tile_start, perm)
+            xs = ws.alloc((A, D), x.dtype)
+            K.moe_gather_rows(x, perm, top, xs)
+            K.moe_tc_gemm(xs, self.gate_up, perm, offsets, tile_start, True, act, limit=self.expert_limit,
+                          alpha=self.act_alpha, shift=self.act_shift)
+            K.moe_tc_gemm(act, self.down, perm, offsets, tile_start, False, y)
+        else:
+            mma = K.moe_gemm_tc_ok(x, self.gate_up) and K.moe_gemm_tc_ok(act, self.down)
+            K.moe_plan(ids, E, "mma" if mma else "float", offsets, tile_start, perm)
+            K.moe_gemm(x, self.gate_up, perm, offsets, tile_start, top, True, act, mma, limit=self.expert_limit,
+                       alpha=self.act_alpha, shift=self.act_shift)
+            K.moe_gemm(act, self.down, perm, offsets, tile_start, top, False, y, mma)
+        if side is not None:
+            main.wait_stream(side)
         K.moe_combine(y, weights, shared, out)
 
     def streamed_weights(self) -> List[Tensor]:

@@ -137,7 +137,7 @@ def save_file(tensors: Mapping[str, torch.Tensor], path: str, metadata: Mapping[
         t = tensors[name].detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise SafetensorsError(f"cannot store dtype {t.dtype} ({name})")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""  # (a tensor may have no dimensions)
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
                         "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)

@@ -77,11 +77,12 @@ TF_C = {
 }
 
 # Sizes at which the tensor-core forms of the kernels are the ones that run: head sizes of 64 and 128
-# (a padded value size), head and state sizes the chunked scan takes, expert rows of whole 16-byte groups.
+# (a padded value size), head and state sizes the chunked scan takes, expert rows of whole 128-byte pieces
+# (the tcgen05 grouped products in prompt steps, the mma.sync ones in decode steps).
 _M_LEFT = {"heads": 8, "kv_heads": 2, "dim": 128, "vdim": 64, "scale": 0.09,
            "rot": {"dims": 64, "base": 100000.0, "scaling": {"factor": 2.0}}}
 _M_RIGHT = {"heads": 8, "vdim": 64, "state": 64, "groups": 2, "conv": 4, "norm_groups": 4}
-_M_MLP = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": 96, "limit": 2.0},
+_M_MLP = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": 128, "limit": 2.0},
           "shared": {"ff": 256, "limit": 4.0}}
 _M_LEFT2 = {"heads": 4, "kv_heads": 4, "dim": 64, "vdim": 64, "scale": 0.125, "rot": {"dims": 32, "base": 10000.0}}
 _M_RIGHT2 = {"heads": 4, "vdim": 32, "state": 128, "groups": 1, "conv": 3, "norm_groups": 1}
@@ -138,13 +139,13 @@ def make_weights(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:
         norm(p + "norm1b", D)
         H, G, d, dv = L["heads"], L["kv_heads"], L["dim"], L["vdim"]
         for name, rows in (("q", H * d), ("k", G * d), ("v", G * dv)):
-            mat(p + "mix.left." + name, rows, D, 2.0)
+            mat(p + "mix.left." + name, rows, D, 1.2)
             vec(p + f"mix.left.{name}.b", (rows,), 0.3)
-        mat(p + "mix.left.g", H * dv, D, 2.0)
+        mat(p + "mix.left.g", H * dv, D, 1.2)
         mat(p + "mix.left.o", D, H * dv)
         Hr, P, N, Gr, taps = R["heads"], R["vdim"], R["state"], R["groups"], R["conv"]
         inner, gn = Hr * P, Gr * N
-        mat(p + "mix.right.in", 2 * inner + 2 * gn + Hr, D, 1.5)
+        mat(p + "mix.right.in", 2 * inner + 2 * gn + Hr, D, 1.0)
         vec(p + "mix.right.conv", (inner + 2 * gn, taps), 0.6)
         vec(p + "mix.right.conv.b", (inner + 2 * gn,), 0.2)
         vec(p + "mix.right.dt_bias", (Hr,), 1.0, -1.0)
@@ -160,13 +161,13 @@ def make_weights(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:
             mat(p + "mlp.router", E, D, 3.0)
             vec(p + "mlp.router.b", (E,), 0.5)
             for e in range(E):
-                mat(p + f"mlp.e{e}.gate", F, D, 2.0)
-                mat(p + f"mlp.e{e}.up", F, D, 2.0)
-                mat(p + f"mlp.e{e}.down", D, F, 1.5)
+                mat(p + f"mlp.e{e}.gate", F, D, 1.2)
+                mat(p + f"mlp.e{e}.up", F, D, 1.2)
+                mat(p + f"mlp.e{e}.down", D, F, 1.0)
             if mlp.get("shared"):
                 Fs = mlp["shared"]["ff"]
-                mat(p + "mlp.shared.gate", Fs, D, 2.0)
-                mat(p + "mlp.shared.up", Fs, D, 2.0)
+                mat(p + "mlp.shared.gate", Fs, D, 1.2)
+                mat(p + "mlp.shared.up", Fs, D, 1.2)
                 mat(p + "mlp.shared.down", D, Fs)
     norm("final.norm", D)
     return {k: v.to(torch.bfloat16).to(torch.float32) for k, v in W.items()}
@@ -188,6 +189,20 @@ def make_model_dir(which, out_dir: str, seed: int = 0, patch=None, edit=None) ->
         json.dump(cfg, fh)
     save_file({k: v.to(torch.bfloat16) for k, v in weights.items()}, os.path.join(out_dir, "model.safetensors"))
     return out_dir, cfg, weights
+
+
+def decisive_routers(weights: Dict[str, torch.Tensor]) -> None:
+    """Routers whose choice no rounding can turn: the logits' spread over tokens becomes small beside gaps of one
+    between the experts' biases (in an order of its own in every layer), so that every token of a layer takes the
+    same experts, with weights that still depend on the token.  bfloat16 runs are compared with the plain
+    implementation under such routers: with freely routed tokens a few per cent of them choose between two
+    experts whose logits differ by less than bfloat16 rounding moves them, and either choice is right."""
+    for name in sorted(weights):
+        if name.endswith("mlp.router"):
+            weights[name] = weights[name] * 0.02
+            E = weights[name].shape[0]
+            order = torch.randperm(E, generator=torch.Generator().manual_seed(len(name) + E))
+            weights[name + ".b"] = order.to(torch.float32) * 1.0 + weights[name + ".b"] * 0.05
 
 
 def sequences(cfg: dict, lengths, seed: int = 0) -> List[List[int]]:
