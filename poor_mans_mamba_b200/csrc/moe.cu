@@ -6,7 +6,7 @@
 //   pairs (t, j) are sorted by expert: offsets[e] .. offsets[e+1] are expert e's rows of `perm`,
 //   perm[i] = t * top + j;
 //   act[i]  = glu(x[perm[i] / top] Wgu_e^T)        [gate | up] rows of expert e, clamped gated activation
-//   y[perm[i]] = act[i] Wd_e^T                     float
+//   y[perm[i]] = act[i] Wd_e^T                     storage type
 //   out[t] = sum_j p[t, j] y[t * top + j] (+ shared[t])
 //
 // Everything stays on the device: the grouped products are launched for an upper bound of row
@@ -17,41 +17,60 @@
 
 namespace pmm {
 
-constexpr int kRouteTokens = 4;  // tokens a warp routes at a time (a router row is read once for them)
+// A block routes TOK tokens: their rows wait in shared memory as floats, every warp takes the experts
+// e = warp, warp + 8, ... and reads a router row once (16 bytes a lane and access) for all TOK dot
+// products; then a warp per token picks the `top` largest logits and norms their exponentials.
+constexpr int kRouteWarps = 8;
 
-template <typename S>
-__global__ void __launch_bounds__(256)
+template <typename S, int TOK>
+__global__ void __launch_bounds__(kRouteWarps * 32)
     moe_route_kernel(const S* __restrict__ x, long long ld_x, const float* __restrict__ w,
                      const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights, int T, int D,
                      int E, int top) {
-  extern __shared__ float route_logits[];  // [warps][kRouteTokens][E]
+  extern __shared__ __align__(16) float route_smem[];  // rows [TOK][Dpad] | logits [TOK][E]
+  const int Dpad = (D + 3) & ~3;
+  float* rows = route_smem;
+  float* logits = route_smem + TOK * Dpad;
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t0 = (blockIdx.x * (blockDim.x >> 5) + warp) * kRouteTokens;
-  if (t0 >= T) return;
-  float* lg = route_logits + static_cast<size_t>(warp) * kRouteTokens * E;
-  const int nt = min(kRouteTokens, T - t0);
-  for (int e = 0; e < E; ++e) {
-    float acc[kRouteTokens];
+  const int t0 = blockIdx.x * TOK;
+  const int nt = min(TOK, T - t0);
+  for (int r = 0; r < TOK; ++r)
+    for (int i = threadIdx.x; i < Dpad; i += blockDim.x)
+      rows[r * Dpad + i] = (r < nt && i < D) ? ldf(x + static_cast<long long>(t0 + r) * ld_x + i) : 0.f;
+  __syncthreads();
+  const bool vec = (D & 3) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+  for (int e = warp; e < E; e += kRouteWarps) {
+    float acc[TOK];
 #pragma unroll
-    for (int r = 0; r < kRouteTokens; ++r) acc[r] = 0.f;
+    for (int r = 0; r < TOK; ++r) acc[r] = 0.f;
     const float* wr = w + static_cast<size_t>(e) * D;
-    for (int i = lane; i < D; i += 32) {
-      const float wv = wr[i];
+    if (vec) {
+      for (int i = lane * 4; i < D; i += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(wr + i);
 #pragma unroll
-      for (int r = 0; r < kRouteTokens; ++r)
-        if (r < nt) acc[r] += ldf(x + static_cast<long long>(t0 + r) * ld_x + i) * wv;
+        for (int r = 0; r < TOK; ++r) {
+          const float4 xv = *reinterpret_cast<const float4*>(rows + r * Dpad + i);
+          acc[r] += xv.x * wv.x + xv.y * wv.y + xv.z * wv.z + xv.w * wv.w;
+        }
+      }
+    } else {
+      for (int i = lane; i < D; i += 32) {
+        const float wv = wr[i];
+#pragma unroll
+        for (int r = 0; r < TOK; ++r) acc[r] += rows[r * Dpad + i] * wv;
+      }
     }
 #pragma unroll
-    for (int r = 0; r < kRouteTokens; ++r) {
-      const float s = warp_sum(acc[r]);
-      if (lane == 0) lg[r * E + e] = s + (bias ? bias[e] : 0.f);
+    for (int r = 0; r < TOK; ++r) {
+      const float sum = warp_sum(acc[r]);
+      if (lane == 0) logits[r * E + e] = sum + (bias ? bias[e] : 0.f);
     }
   }
-  __syncwarp();
-  for (int r = 0; r < nt; ++r) {
-    float* z = lg + r * E;
+  __syncthreads();
+  for (int r = warp; r < nt; r += kRouteWarps) {
+    float* z = logits + r * E;
     float first = 0.f, denom = 0.f;
     for (int j = 0; j < top; ++j) {
       float best = -INFINITY;
@@ -60,14 +79,13 @@ __global__ void __launch_bounds__(256)
         const float v = z[e];
         if (v > best || (v == best && e < arg)) { best = v; arg = e; }
       }
-      if (arg == 0x7fffffff) arg = 0x7ffffffe;  // a lane without a candidate
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         const float ob = __shfl_xor_sync(0xffffffffu, best, o);
         const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
         if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
       }
-      if (arg >= E) arg = j;  // every logit is NaN or -inf: keep the indices valid
+      if (arg >= E) arg = j;  // every logit left is NaN or -inf: keep the indices valid
       if (j == 0) first = best;
       const float p = expf(best - first);
       denom += p;
@@ -111,35 +129,33 @@ __global__ void __launch_bounds__(1024)
 }
 
 // One block per expert: its pairs in the order of their index (stable, so the plan is the same every time).
-__global__ void __launch_bounds__(256)
+// A thread owns a run of consecutive pairs: it counts its matches, the block sums the counts before each
+// thread, and the thread writes its matches from there.
+__global__ void __launch_bounds__(1024)
     moe_fill_kernel(const int* __restrict__ ids, int A, const int* __restrict__ offsets, int* __restrict__ perm) {
-  __shared__ int warp_count[8];
-  __shared__ int running;
+  __shared__ int warp_total[32];
   pdl_launch_dependents();
   pdl_wait();
   const int e = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int base = offsets[e];
   if (offsets[e + 1] == base) return;
-  if (threadIdx.x == 0) running = 0;
-  __syncthreads();
-  for (int start = 0; start < A; start += 256) {
-    const int i = start + threadIdx.x;
-    const bool mine = i < A && ids[i] == e;
-    const unsigned ballot = __ballot_sync(0xffffffffu, mine);
-    if (lane == 0) warp_count[warp] = __popc(ballot);
-    __syncthreads();
-    int before = running;
-    for (int w2 = 0; w2 < warp; ++w2) before += warp_count[w2];
-    if (mine) perm[base + before + __popc(ballot & ((1u << lane) - 1u))] = i;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int total = 0;
-      for (int w2 = 0; w2 < 8; ++w2) total += warp_count[w2];
-      running += total;
-    }
-    __syncthreads();
+  const int run = (A + blockDim.x - 1) / blockDim.x;
+  const int i0 = min(A, static_cast<int>(threadIdx.x) * run), i1 = min(A, i0 + run);
+  int mine = 0;
+  for (int i = i0; i < i1; ++i) mine += ids[i] == e;
+  int incl = mine;  // inclusive sum over the warp
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
   }
+  if (lane == 31) warp_total[warp] = incl;
+  __syncthreads();
+  int before = base + incl - mine;
+  for (int w2 = 0; w2 < warp; ++w2) before += warp_total[w2];
+  for (int i = i0; i < i1; ++i)
+    if (ids[i] == e) perm[before++] = i;
 }
 
 // The whole plan of a step with few pairs (a decode step) in one block and one launch: a thread per expert
@@ -207,7 +223,7 @@ __device__ __forceinline__ bool moe_tile(int tile, const int* __restrict__ offse
 // The grouped product in float arithmetic on the CUDA cores, for any sizes and both storage types.
 // UP (the [gate | up] product with the activation): a = x [T, K], row i reads x[perm[i] / top]; w [E, 2N, K];
 // out = act [A, N] in the storage type.  Otherwise (the down product): a = act [A, K]; w [E, N, K];
-// out = y [A, N] float, row perm[i].
+// out = y [A, N] in the storage type, row perm[i].
 constexpr int kGenRows = 32, kGenCols = 32, kGenK = 32;
 
 template <typename S, bool UP>
@@ -271,7 +287,7 @@ __global__ void __launch_bounds__(256)
       stf(static_cast<S*>(out) + static_cast<size_t>(i) * N + n0 + tx,
           clamped_glu(acc[0][r], acc[UP ? 1 : 0][r], limit, alpha, shift));
     } else {
-      static_cast<float*>(out)[static_cast<size_t>(perm[i]) * N + n0 + tx] = acc[0][r];
+      stf(static_cast<S*>(out) + static_cast<size_t>(perm[i]) * N + n0 + tx, acc[0][r]);
     }
   }
 }
@@ -376,17 +392,125 @@ __global__ void __launch_bounds__(128)
           const float g = acc[j][half * 2 + q], u = acc[UP ? j + kMmaCols / 8 : j][half * 2 + q];
           static_cast<bf16*>(out)[static_cast<size_t>(i) * N + col] = __float2bfloat16_rn(clamped_glu(g, u, limit, alpha, shift));
         } else {
-          static_cast<float*>(out)[static_cast<size_t>(dst_row[r]) * N + col] = acc[j][half * 2 + q];
+          static_cast<bf16*>(out)[static_cast<size_t>(dst_row[r]) * N + col] = __float2bfloat16_rn(acc[j][half * 2 + q]);
         }
       }
     }
   }
 }
 
-// out[t] = sum_j p[t, j] y[t * top + j] (+ shared[t]); y float, shared and out in the storage type.
+// The same product for steps of few pairs (decode steps), where an expert has a handful of rows and the
+// launch is a read of the chosen experts' matrices: tiles of 16 rows x 64 columns, the four warps share the
+// columns, K in slices of 64 through a four-stage ring, so that a block keeps three slices in flight.
+constexpr int kFewRows = 16, kFewCols = 64, kFewK = 64, kFewStages = 4, kFewLd = kFewK + 8;
+
+template <bool UP>
+__global__ void __launch_bounds__(128)
+    moe_gemm_few_kernel(const bf16* __restrict__ a, long long ld_a, const bf16* __restrict__ w,
+                        const int* __restrict__ perm, const int* __restrict__ offsets,
+                        const int* __restrict__ tile_start, int E, int top, int K, int N, float limit, float alpha,
+                        float shift, bf16* __restrict__ out) {
+  constexpr int BROWS = UP ? 2 * kFewCols : kFewCols;
+  constexpr int kStageElems = (kFewRows + BROWS) * kFewLd;
+  extern __shared__ __align__(16) unsigned char few_smem[];
+  bf16* ring = reinterpret_cast<bf16*>(few_smem);
+  __shared__ int src_row[kFewRows];
+  __shared__ int dst_row[kFewRows];
+  pdl_launch_dependents();
+  pdl_wait();
+  int e, row0, row1;
+  if (!moe_tile(blockIdx.y, offsets, tile_start, E, kFewRows, e, row0, row1)) return;
+  const int n0 = blockIdx.x * kFewCols;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x < kFewRows) {
+    const int i = row0 + threadIdx.x;
+    const int p = i < row1 ? perm[i] : -1;
+    src_row[threadIdx.x] = i < row1 ? (UP ? p / top : i) : -1;
+    dst_row[threadIdx.x] = p;
+  }
+  __syncthreads();
+  const bf16* we = w + static_cast<size_t>(e) * (UP ? 2 : 1) * N * K;
+
+  auto stage = [&](int buf, int k0) {
+    bf16* As = ring + static_cast<size_t>(buf) * kStageElems;
+    bf16* Bs = As + kFewRows * kFewLd;
+    {  // 16 rows x 8 pieces of 8 elements: one a thread
+      const int r = threadIdx.x >> 3, c = (threadIdx.x & 7) * 8;
+      const int src = src_row[r];
+      const bool ok = src >= 0 && k0 + c < K;
+      cp_async16(As + r * kFewLd + c, ok ? a + static_cast<long long>(src) * ld_a + k0 + c : a, ok);
+    }
+    for (int idx = threadIdx.x; idx < BROWS * 8; idx += 128) {
+      const int r = idx >> 3, c = (idx & 7) * 8;
+      const int col = UP ? (r < kFewCols ? n0 + r : n0 + r - kFewCols) : n0 + r;
+      const bool ok = col < N && k0 + c < K;
+      const size_t wrow = UP && r >= kFewCols ? static_cast<size_t>(N) + col : col;
+      cp_async16(Bs + r * kFewLd + c, ok ? we + wrow * K + k0 + c : we, ok);
+    }
+    cp_async_commit();
+  };
+
+  float acc[UP ? 4 : 2][4];
+#pragma unroll
+  for (int j = 0; j < (UP ? 4 : 2); ++j)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) acc[j][q] = 0.f;
+
+  const int n_slices = (K + kFewK - 1) / kFewK;
+#pragma unroll
+  for (int s = 0; s < kFewStages - 1; ++s) {
+    if (s < n_slices) stage(s, s * kFewK);
+    else cp_async_commit();
+  }
+  for (int s = 0; s < n_slices; ++s) {
+    cp_async_wait<kFewStages - 2>();  // slice s has landed
+    __syncthreads();                  // ... for every thread, and slice s - 1's buffer is free
+    if (s + kFewStages - 1 < n_slices) stage((s + kFewStages - 1) % kFewStages, (s + kFewStages - 1) * kFewK);
+    else cp_async_commit();
+    const bf16* As = ring + static_cast<size_t>(s % kFewStages) * kStageElems;
+    const bf16* Bs = As + kFewRows * kFewLd;
+#pragma unroll
+    for (int kk = 0; kk < kFewK; kk += 16) {
+      unsigned af[4];
+      ldmatrix_x4(af[0], af[1], af[2], af[3], As + (lane & 15) * kFewLd + kk + ((lane >> 4) << 3));
+#pragma unroll
+      for (int part = 0; part < (UP ? 2 : 1); ++part) {
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3,
+                    Bs + (part * kFewCols + warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * kFewLd + kk + (((lane >> 3) & 1) << 3));
+        mma_bf16(acc[2 * part], af, b0, b1);
+        mma_bf16(acc[2 * part + 1], af, b2, b3);
+      }
+    }
+  }
+
+  const int c_in = (lane & 3) * 2;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = (lane >> 2) + half * 8;
+    const int i = row0 + r;
+    if (i >= row1) continue;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int col = n0 + warp * 16 + j * 8 + c_in + q;
+        if (col >= N) continue;
+        if (UP) {
+          out[static_cast<size_t>(i) * N + col] =
+              __float2bfloat16_rn(clamped_glu(acc[j][half * 2 + q], acc[UP ? 2 + j : j][half * 2 + q], limit, alpha, shift));
+        } else {
+          out[static_cast<size_t>(dst_row[r]) * N + col] = __float2bfloat16_rn(acc[j][half * 2 + q]);
+        }
+      }
+    }
+  }
+}
+
+// out[t] = sum_j p[t, j] y[t * top + j] (+ shared[t]); y, shared and out in the storage type, the sum in float.
 template <typename S>
 __global__ void __launch_bounds__(256)
-    moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, const S* __restrict__ shared,
+    moe_combine_kernel(const S* __restrict__ y, const float* __restrict__ weights, const S* __restrict__ shared,
                        S* __restrict__ out, int D, int top) {
   pdl_launch_dependents();
   pdl_wait();
@@ -394,7 +518,7 @@ __global__ void __launch_bounds__(256)
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < D; i += gridDim.y * blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < top; ++j)
-      acc += weights[static_cast<size_t>(t) * top + j] * y[(static_cast<size_t>(t) * top + j) * D + i];
+      acc += weights[static_cast<size_t>(t) * top + j] * ldf(y + (static_cast<size_t>(t) * top + j) * D + i);
     if (shared) acc += ldf(shared + static_cast<size_t>(t) * D + i);
     stf(out + static_cast<size_t>(t) * D + i, acc);
   }
@@ -402,24 +526,35 @@ __global__ void __launch_bounds__(256)
 
 }  // namespace pmm
 
+namespace pmm {
+template <typename S, int TOK>
+int launch_route(const void* x, long long ld_x, const float* w, const float* bias, int* ids, float* weights, int T, int D,
+                 int E, int top, cudaStream_t stream) {
+  const size_t smem = (static_cast<size_t>(TOK) * ((D + 3) & ~3) + static_cast<size_t>(TOK) * E) * sizeof(float);
+  if (smem > 200 * 1024) return PMM_ERR_BAD_ARGUMENT;
+  auto kern = moe_route_kernel<S, TOK>;
+  if (smem > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err != cudaSuccess) return static_cast<int>(err);
+  }
+  launch_pdl(kern, dim3((T + TOK - 1) / TOK), dim3(kRouteWarps * 32), smem, stream, static_cast<const S*>(x), ld_x, w, bias,
+             ids, weights, T, D, E, top);
+  return launch_status();
+}
+}  // namespace pmm
+
 PMM_EXPORT int pmm_moe_route(const void* x, long long ld_x, const float* w, const float* bias, int* ids, float* weights,
                              int T, int D, int E, int top, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (D <= 0 || E <= 0 || top <= 0 || top > E) return PMM_ERR_BAD_ARGUMENT;
-  const int warps = 8;
-  const size_t smem = static_cast<size_t>(warps) * pmm::kRouteTokens * E * sizeof(float);
-  if (smem > 200 * 1024) return PMM_ERR_BAD_ARGUMENT;
-  const int per_block = warps * pmm::kRouteTokens;
+  // few tokens: a block each, so that the step's few rows still spread over the GPU; many: four a block, which
+  // reads the router a quarter as often
+  const bool four = T >= 512 && (static_cast<size_t>(4) * (((D + 3) & ~3) + E)) * sizeof(float) <= 96 * 1024;
   PMM_DISPATCH_DTYPE(dtype, S, {
-    auto kern = pmm::moe_route_kernel<S>;
-    if (smem > 48 * 1024) {
-      cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-      if (err != cudaSuccess) return static_cast<int>(err);
-    }
-    pmm::launch_pdl(kern, dim3((T + per_block - 1) / per_block), dim3(warps * 32), smem, stream,
-                    static_cast<const S*>(x), ld_x, w, bias, ids, weights, T, D, E, top);
+    if (four) return pmm::launch_route<S, 4>(x, ld_x, w, bias, ids, weights, T, D, E, top, stream);
+    return pmm::launch_route<S, 1>(x, ld_x, w, bias, ids, weights, T, D, E, top, stream);
   });
-  return pmm::launch_status();
+  return 0;
 }
 
 // ids [A] -> offsets [E + 1], tile_start [E + 1] (row tiles of `tile_rows`), perm [A].  One launch for up to
@@ -437,14 +572,17 @@ PMM_EXPORT int pmm_moe_plan(const int* ids, int A, int E, int tile_rows, int* of
                   tile_rows, offsets, tile_start);
   int rc = pmm::launch_status();
   if (rc != 0) return rc;
-  pmm::launch_pdl(pmm::moe_fill_kernel, dim3(E), dim3(256), 0, stream, ids, A, static_cast<const int*>(offsets), perm);
+  pmm::launch_pdl(pmm::moe_fill_kernel, dim3(E), dim3(1024), 0, stream, ids, A, static_cast<const int*>(offsets), perm);
   return pmm::launch_status();
 }
 
-PMM_EXPORT int pmm_moe_tile_rows(int tensor_cores) { return tensor_cores ? pmm::kMmaRows : pmm::kGenRows; }
+// 0: float products on the CUDA cores, 1: mma.sync tiles, 2: mma.sync tiles for few pairs
+PMM_EXPORT int pmm_moe_tile_rows(int tensor_cores) {
+  return tensor_cores == 2 ? pmm::kFewRows : tensor_cores ? pmm::kMmaRows : pmm::kGenRows;
+}
 
 // up != 0: a = x [T, K] (ld_a), w [E, 2N, K], out act [A, N] (storage type).  up == 0: a = act [A, K], w [E, N, K],
-// out y [A, N] float.  tensor_cores != 0 needs bfloat16, K % 8 == 0, ld_a % 8 == 0 and 16-byte aligned a, w; the
+// out y [A, N] in the storage type.  tensor_cores != 0 needs bfloat16, K % 8 == 0, ld_a % 8 == 0 and 16-byte aligned a, w; the
 // plan must have been made with pmm_moe_tile_rows(tensor_cores) rows a tile.
 PMM_EXPORT int pmm_moe_gemm(const void* a, long long ld_a, const void* w, const int* perm, const int* offsets,
                             const int* tile_start, int A, int E, int top, int K, int N, int up, float limit, float alpha,
@@ -458,6 +596,28 @@ PMM_EXPORT int pmm_moe_gemm(const void* a, long long ld_a, const void* w, const 
     if (dtype != PMM_DTYPE_BF16 || K % 8 || ld_a % 8 || reinterpret_cast<uintptr_t>(a) % 16 ||
         reinterpret_cast<uintptr_t>(w) % 16)
       return PMM_ERR_BAD_ARGUMENT;
+    if (tensor_cores == 2) {
+      const dim3 grid((N + pmm::kFewCols - 1) / pmm::kFewCols, row_tiles);
+      const size_t smem = static_cast<size_t>(pmm::kFewStages) * (pmm::kFewRows + (up ? 2 : 1) * pmm::kFewCols) *
+                          pmm::kFewLd * sizeof(pmm::bf16);
+      cudaError_t err;
+      if (up) {
+        auto kern = pmm::moe_gemm_few_kernel<true>;
+        err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (err != cudaSuccess) return static_cast<int>(err);
+        pmm::launch_pdl(kern, grid, dim3(128), smem, stream, static_cast<const pmm::bf16*>(a), ld_a,
+                        static_cast<const pmm::bf16*>(w), perm, offsets, tile_start, E, top, K, N, limit, alpha, shift,
+                        static_cast<pmm::bf16*>(out));
+      } else {
+        auto kern = pmm::moe_gemm_few_kernel<false>;
+        err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (err != cudaSuccess) return static_cast<int>(err);
+        pmm::launch_pdl(kern, grid, dim3(128), smem, stream, static_cast<const pmm::bf16*>(a), ld_a,
+                        static_cast<const pmm::bf16*>(w), perm, offsets, tile_start, E, top, K, N, limit, alpha, shift,
+                        static_cast<pmm::bf16*>(out));
+      }
+      return pmm::launch_status();
+    }
     const dim3 grid((N + pmm::kMmaCols - 1) / pmm::kMmaCols, row_tiles);
     if (up)
       pmm::launch_pdl(pmm::moe_gemm_mma_kernel<true>, grid, dim3(128), 0, stream, static_cast<const pmm::bf16*>(a), ld_a,
@@ -479,13 +639,13 @@ PMM_EXPORT int pmm_moe_gemm(const void* a, long long ld_a, const void* w, const 
   return pmm::launch_status();
 }
 
-PMM_EXPORT int pmm_moe_combine(const float* y, const float* weights, const void* shared, void* out, int T, int D, int top,
+PMM_EXPORT int pmm_moe_combine(const void* y, const float* weights, const void* shared, void* out, int T, int D, int top,
                                int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (D <= 0 || top <= 0) return PMM_ERR_BAD_ARGUMENT;
   int ytiles = (D + 1023) / 1024;
   if (ytiles > 64) ytiles = 64;
-  PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::moe_combine_kernel<S>, dim3(T, ytiles), dim3(256), 0, stream, y,
-                                               weights, static_cast<const S*>(shared), static_cast<S*>(out), D, top));
+  PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::moe_combine_kernel<S>, dim3(T, ytiles), dim3(256), 0, stream,
+                                               static_cast<const S*>(y), weights, static_cast<const S*>(shared), static_cast<S*>(out), D, top));
   return pmm::launch_status();
 }

@@ -3,7 +3,7 @@
 // tile of 128 rows belongs to one expert and may be ragged at its end.
 //
 //   up:    act[i, f] = glu((xs W_gate,e^T)[i, f], (xs W_up,e^T)[i, f])     xs = the token rows in sorted order
-//   down:  y[perm[i], :] = act[i] W_down,e^T                               float
+//   down:  y[perm[i], :] = act[i] W_down,e^T
 //
 // One block computes 128 rows x 256 accumulator columns (up: 128 gate columns beside their 128 up
 // columns; down: 256 output columns).  Structure as in tc_gemm.cu: a TMA producer warp fills a ring
@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(kGThreads)
           }
         }
       } else {
-        float* dst_row = static_cast<float*>(out) + static_cast<size_t>(row_ok ? perm[i] : 0) * N;
+        bf16* dst_row = static_cast<bf16*>(out) + static_cast<size_t>(row_ok ? perm[i] : 0) * N;
 #pragma unroll 1
         for (int q = 0; q < kGN / 32; ++q) {
           unsigned v[32];
@@ -190,11 +190,16 @@ __global__ void __launch_bounds__(kGThreads)
           asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
           if (row_ok) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
+            for (int j = 0; j < 32; j += 8) {
               const int col = n0 + q * 32 + j;
-              if (col < N)  // N is a multiple of 8
-                *reinterpret_cast<float4*>(dst_row + col) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                                         __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+              if (col < N) {  // N is a multiple of 8
+                uint4 pack;
+                __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pack);
+#pragma unroll
+                for (int h = 0; h < 4; ++h)
+                  p2[h] = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * h]), __uint_as_float(v[j + 2 * h + 1]));
+                *reinterpret_cast<uint4*>(dst_row + col) = pack;
+              }
             }
           }
         }
@@ -257,7 +262,7 @@ PMM_EXPORT int pmm_moe_gather_rows(const void* x, long long ld_x, const int* per
 
 // a [A, K] bfloat16 rows in the order of the sorted pairs (row stride ld_a); w the experts' stacked matrices
 // [E * (up ? 2N : N), K]; the plan made with rows of pmm_moe_tc_tile_rows().  up: out = act [A, N] bfloat16;
-// else out = y [A, N] float, row perm[i].  status: one int, stays 0 unless a bounded wait gave up.
+// else out = y [A, N] bfloat16, row perm[i].  status: one int, stays 0 unless a bounded wait gave up.
 PMM_EXPORT int pmm_moe_tc_gemm(const void* a, long long ld_a, const void* w, const int* perm, const int* offsets,
                                const int* tile_start, int A, int E, int K, int N, int up, float limit, float alpha,
                                float shift, void* out, int* status, cudaStream_t stream) {

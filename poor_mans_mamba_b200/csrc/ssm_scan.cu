@@ -222,7 +222,7 @@ template <typename S, typename Y>
 __global__ void gated_norm_kernel(const Y* __restrict__ y, const S* __restrict__ z_raw,
                                   long long ld_z, float z_scale, const float* __restrict__ z_bias,
                                   const float* __restrict__ w, float eps, int norm_before_gate,
-                                  S* __restrict__ out, int I, int group_width, int gate_sigmoid) {
+                                  S* __restrict__ out, long long ld_out, int I, int group_width, int gate_sigmoid) {
   extern __shared__ float buf[];
   __shared__ float red[32];
   pdl_launch_dependents();
@@ -237,7 +237,7 @@ __global__ void gated_norm_kernel(const Y* __restrict__ y, const S* __restrict__
     const float gate = gate_sigmoid ? 1.f / (1.f + expf(-zv)) : silu_f(zv);
     float v;
     if (!w) {
-      stf(out + static_cast<size_t>(t) * I + c, yv * gate);
+      stf(out + static_cast<long long>(t) * ld_out + c, yv * gate);
       continue;
     }
     if (norm_before_gate) {
@@ -256,7 +256,7 @@ __global__ void gated_norm_kernel(const Y* __restrict__ y, const S* __restrict__
     const int c = c0 + i;
     float v = buf[i] * inv * w[c];
     if (norm_before_gate) v *= buf[group_width + i];
-    stf(out + static_cast<size_t>(t) * I + c, v);
+    stf(out + static_cast<long long>(t) * ld_out + c, v);
   }
 }
 
@@ -324,8 +324,8 @@ PMM_EXPORT int pmm_ssm_scan_seq(const void* xbc, int ld_xbc, const void* dt_raw,
 
 PMM_EXPORT int pmm_gated_norm(const void* y, const void* z_raw, long long ld_z, float z_scale,
                               const float* z_bias, const float* w, float eps, int norm_before_gate,
-                              void* out, int T, int I, int n_groups, int dtype, int y_f32, int gate_sigmoid,
-                              cudaStream_t stream) {
+                              void* out, long long ld_out, int T, int I, int n_groups, int dtype, int y_f32,
+                              int gate_sigmoid, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (n_groups <= 0 || I % n_groups || n_groups > 65535) return PMM_ERR_BAD_ARGUMENT;
   const int gw = I / n_groups;
@@ -341,7 +341,7 @@ PMM_EXPORT int pmm_gated_norm(const void* y, const void* z_raw, long long ld_z, 
       if (e != cudaSuccess) return static_cast<int>(e);                                                            \
     }                                                                                                              \
     pmm::launch_pdl(kern, grid, dim3(256), smem, stream, static_cast<const Y*>(y), static_cast<const S*>(z_raw),   \
-                    ld_z, z_scale, z_bias, w, eps, norm_before_gate, static_cast<S*>(out), I, gw, gate_sigmoid);   \
+                    ld_z, z_scale, z_bias, w, eps, norm_before_gate, static_cast<S*>(out), ld_out, I, gw, gate_sigmoid);   \
   } while (0)
   // y_f32: the rows to norm are floats whatever the storage type (a recurrence's output)
   PMM_DISPATCH_DTYPE(dtype, S, {

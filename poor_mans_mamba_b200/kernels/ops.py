@@ -51,7 +51,7 @@ _SIGNATURES = {
                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                    c_longlong, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "pmm_gated_norm": [c_void_p, c_void_p, c_longlong, c_float, c_void_p, c_void_p, c_float, c_int,
-                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                       c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "pmm_qkv_rope_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_float,
                            c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                            c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -740,12 +740,12 @@ def gated_norm(y: Tensor, z_raw: Tensor, z_scale: float, z_bias: Optional[Tensor
                out: Tensor, gate: str = "silu") -> None:
     """out = y*silu(z), optionally RMS-normalised per group of channels (before or after the gate).
     ``gate`` "sigmoid": sigmoid(z) in place of silu(z).  y may be float32 whatever the type of z and
-    out (a recurrence's output)."""
+    out (a recurrence's output); out may be a column block of a wider matrix."""
     _cuda(y, z_raw, z_bias, weight, out)
     T, I = y.shape
-    if not (y.is_contiguous() and out.is_contiguous() and out.shape == y.shape
+    if not (y.is_contiguous() and out.dim() == 2 and out.stride(1) == 1 and out.shape == y.shape
             and y.dtype in (out.dtype, torch.float32)):
-        raise KernelError("gated_norm: y and out must be contiguous [T, I]; y of out's type or float32")
+        raise KernelError("gated_norm: y contiguous [T, I], out [T, I] with unit column stride; y of out's type or float32")
     if gate not in ("silu", "sigmoid"):
         raise KernelError("gated_norm: the gate is 'silu' or 'sigmoid'")
     ld_z = _rows_view(z_raw, "gated_norm: z")
@@ -757,7 +757,7 @@ def gated_norm(y: Tensor, z_raw: Tensor, z_scale: float, z_bias: Optional[Tensor
     if not (I % groups == 0):
         raise KernelError("gated_norm: width must be a multiple of the group count")
     _call("pmm_gated_norm", y.data_ptr(), z_raw.data_ptr(), ld_z, float(z_scale), _ptr(z_bias),
-          _ptr(weight), float(eps), int(bool(norm_before_gate)), out.data_ptr(), T, I, groups, _dt(out),
+          _ptr(weight), float(eps), int(bool(norm_before_gate)), out.data_ptr(), out.stride(0), T, I, groups, _dt(out),
           int(y.dtype == torch.float32 and out.dtype != torch.float32), int(gate == "sigmoid"), _stream())
 
 
@@ -1454,12 +1454,15 @@ def moe_route(x: Tensor, router_w: Tensor, router_b: Optional[Tensor], top: int,
           weights.data_ptr(), T, D, E, int(top), _dt(x), _stream())
 
 
+_MOE_FORMS = {"float": 0, "mma": 1, "mma_few": 2}
+
+
 def moe_tile_rows(form: str) -> int:
-    """Rows of a row tile of the grouped products: ``form`` "float" (CUDA cores, any sizes), "mma" (mma.sync) or
-    "tcgen05"."""
+    """Rows of a row tile of the grouped products: ``form`` "float" (CUDA cores, any sizes), "mma" (mma.sync),
+    "mma_few" (mma.sync, steps of few pairs) or "tcgen05"."""
     if form == "tcgen05":
         return int(_fn("pmm_moe_tc_tile_rows")())
-    return int(_fn("pmm_moe_tile_rows")(int(form == "mma")))
+    return int(_fn("pmm_moe_tile_rows")(_MOE_FORMS[form]))
 
 
 def moe_plan(ids: Tensor, n_experts: int, form: str, offsets: Tensor, tile_start: Tensor, perm: Tensor) -> None:
@@ -1499,13 +1502,13 @@ def moe_tc_gemm(a: Tensor, w: Tensor, perm: Tensor, offsets: Tensor, tile_start:
                 limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0) -> None:
     """The grouped product on the fifth-generation tensor cores.  a [pairs, K]: rows in the order of the sorted
     pairs (the gathered token rows, or the activation); w [E, N (2N), K]; the plan made for "tcgen05" row tiles.
-    ``up``: out = act [pairs, N] bfloat16 with the clamped gated activation; else out = y [pairs, N] float32 in
-    the order of the pairs."""
+    ``up``: out = act [pairs, N] with the clamped gated activation; else out = y [pairs, N] in the order of the
+    pairs (both bfloat16)."""
     _cuda(a, w, perm, offsets, tile_start, out)
     A, Kd = a.shape
     E, N = w.shape[0], out.shape[1]
     if not (w.dim() == 3 and w.is_contiguous() and w.shape == (E, (2 if up else 1) * N, Kd) and perm.numel() == A
-            and out.shape == (A, N) and out.is_contiguous() and out.dtype == (torch.bfloat16 if up else torch.float32)
+            and out.shape == (A, N) and out.is_contiguous() and out.dtype == torch.bfloat16
             and offsets.numel() == E + 1 and tile_start.numel() == E + 1 and moe_tc_supported(a, w, N)):
         raise KernelError("moe_tc_gemm: operands outside what the kernel takes")
     _call("pmm_moe_tc_gemm", a.data_ptr(), a.stride(0), w.data_ptr(), perm.data_ptr(), offsets.data_ptr(),
@@ -1520,10 +1523,10 @@ def moe_gemm_tc_ok(a: Tensor, w: Tensor) -> bool:
 
 
 def moe_gemm(a: Tensor, w: Tensor, perm: Tensor, offsets: Tensor, tile_start: Tensor, top: int, up: bool, out: Tensor,
-             tensor_cores: bool, limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0) -> None:
+             form: str, limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0) -> None:
     """Grouped product over the rows of a plan.  ``up``: a = x [T, K], w [E, 2N, K] ([gate | up] rows of
     every expert), out = act [T*top, N] in the storage type, with the clamped gated activation.  Else:
-    a = act [T*top, K], w [E, N, K], out = y [T*top, N] float32 in the order of the pairs."""
+    a = act [T*top, K], w [E, N, K], out = y [T*top, N] in the order of the pairs."""
     _cuda(a, w, perm, offsets, tile_start, out)
     A = perm.numel()
     E = w.shape[0]
@@ -1531,15 +1534,16 @@ def moe_gemm(a: Tensor, w: Tensor, perm: Tensor, offsets: Tensor, tile_start: Te
     N = out.shape[1]
     if not (w.dim() == 3 and w.is_contiguous() and w.shape == (E, (2 if up else 1) * N, K) and w.dtype == a.dtype):
         raise KernelError("moe_gemm: w must be contiguous [E, N (2N for the gate and up rows), K] of a's type")
-    if not (out.shape == (A, N) and out.is_contiguous() and out.dtype == (a.dtype if up else torch.float32)):
-        raise KernelError("moe_gemm: out [pairs, N], the storage type for the activation, float32 for the result")
+    if not (out.shape == (A, N) and out.is_contiguous() and out.dtype == a.dtype):
+        raise KernelError("moe_gemm: out [pairs, N] of the operands' type")
     if not (a.shape[0] == (A // top if up else A) and offsets.numel() == E + 1 and tile_start.numel() == E + 1):
         raise KernelError("moe_gemm: rows of a, offsets or tile_start do not fit the plan")
+    tensor_cores = _MOE_FORMS[form]  # the plan must have been made for the same form
     if tensor_cores and not moe_gemm_tc_ok(a, w):
-        raise KernelError("moe_gemm: the tensor-core form needs bfloat16, K a multiple of 8 and 16-byte aligned rows")
+        raise KernelError("moe_gemm: the tensor-core forms need bfloat16, K a multiple of 8 and 16-byte aligned rows")
     _call("pmm_moe_gemm", a.data_ptr(), _rows_view(a, "moe_gemm"), w.data_ptr(), perm.data_ptr(), offsets.data_ptr(),
           tile_start.data_ptr(), A, E, int(top), K, N, int(bool(up)), float(limit), float(alpha), float(shift),
-          out.data_ptr(), int(bool(tensor_cores)), _dt(a), _stream())
+          out.data_ptr(), tensor_cores, _dt(a), _stream())
 
 
 def moe_combine(y: Tensor, weights: Tensor, shared: Optional[Tensor], out: Tensor) -> None:
@@ -1547,9 +1551,9 @@ def moe_combine(y: Tensor, weights: Tensor, shared: Optional[Tensor], out: Tenso
     _cuda(y, weights, shared, out)
     T, top = weights.shape
     D = out.shape[1]
-    if not (y.shape == (T * top, D) and y.dtype == torch.float32 and y.is_contiguous() and out.shape == (T, D)
+    if not (y.shape == (T * top, D) and y.dtype == out.dtype and y.is_contiguous() and out.shape == (T, D)
             and out.is_contiguous() and weights.dtype == torch.float32 and weights.is_contiguous()):
-        raise KernelError("moe_combine: y [T*top, D] float32, weights [T, top] float32, out contiguous [T, D]")
+        raise KernelError("moe_combine: y [T*top, D] of out's type, weights [T, top] float32, out contiguous [T, D]")
     if shared is not None and not (shared.shape == (T, D) and shared.is_contiguous() and shared.dtype == out.dtype):
         raise KernelError("moe_combine: shared must be contiguous [T, D] of out's type")
     _call("pmm_moe_combine", y.data_ptr(), weights.data_ptr(), _ptr(shared), out.data_ptr(), T, D, top, _dt(out), _stream())

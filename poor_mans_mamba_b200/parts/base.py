@@ -186,6 +186,17 @@ class Mixer(Part):
     def output_weight(self) -> Optional[Tensor]:
         return None
 
+    def pre_output_into(self, proj: Tensor, ctx, cache: LayerCache, into: Tensor, scale: float) -> bool:
+        """Writes scale * (the activation that ``output_weight`` is applied to) into ``into`` [T, inner], a
+        column block of a wider matrix, and returns True; False (nothing done) where the mixer cannot.  An
+        arrangement whose mixers all can runs their output projections as ONE product over the joined
+        columns, sum_m scale_m * y_m W_m^T = [scale_0 y_0 | scale_1 y_1 | ...] [W_0 | W_1 | ...]^T."""
+        return False
+
+    def joins_output_products(self) -> bool:
+        """Whether `pre_output_into` is available for this mixer as it is configured."""
+        return False
+
     def output_bias(self) -> Optional[Tensor]:
         return None
 

@@ -29,6 +29,9 @@ Tensor = torch.Tensor
 # The mixers of a layer on parallel streams in steps of many tokens too (PMM_PARALLEL_MIXERS=0: one
 # after the other).
 _PARALLEL_MIXERS = os.environ.get("PMM_PARALLEL_MIXERS", "1") == "1"
+# With a post norm: the mixers' output projections as one product over their joined columns
+# (PMM_JOINED_OUTPUTS=0: one product a mixer).
+_JOINED_OUTPUTS = os.environ.get("PMM_JOINED_OUTPUTS", "1") == "1"
 
 
 def prenorm_layer(prefix: str, mixer_norm: PartSpec, mixers, ffn_norm: Optional[PartSpec] = None,
@@ -185,6 +188,8 @@ class ParallelPreNormBlock(Part):
                 self.ffn_post_norm = build_part("norm", spec.part("ffn_post_norm"), width=hidden_size)
         self._fused_in: Optional[Tensor] = None
         self._fused_cols: List[Tuple[int, int]] = []
+        self._fused_out: Optional[Tensor] = None   # [D, sum of the mixers' inner widths], see Mixer.pre_output_into
+        self._fused_out_cols: List[Tuple[int, int]] = []
 
     def parts(self) -> List[Part]:
         out: List[Part] = [self.mixer_norm, *self.mixers]
@@ -218,6 +223,17 @@ class ParallelPreNormBlock(Part):
                 self._fused_cols.append((start, start + rows))
                 start += rows
             self._fused_in = fused
+            # With a post norm the mixers' results join as one sum anyway: their output projections run as
+            # one product over the joined columns where every mixer can write its scaled activation there.
+            if (self.mixer_post_norm is not None and _JOINED_OUTPUTS
+                    and all(m.joins_output_products() and m.output_weight() is not None and m.output_bias() is None
+                            for m in self.mixers)):
+                self._fused_out = torch.cat([m.output_weight() for m in self.mixers], dim=1).contiguous()
+                start = 0
+                for m in self.mixers:
+                    k = int(m.output_weight().shape[1])
+                    self._fused_out_cols.append((start, start + k))
+                    start += k
 
     def _few_tokens_path(self, ctx) -> bool:
         """Steps of few tokens in bfloat16 are reads of the weights: they take the fused
@@ -317,23 +333,40 @@ class ParallelPreNormBlock(Part):
             # The mixers only share their input.  With several, the first runs on a side stream
             # beside the others (parallel branches of a captured step): a prompt portion's scan and
             # attention are each a chain of launches with few blocks, and together they fill the GPU.
-            outs = [stream.take_branch() for _ in self.mixers]
+            joined = None
+            if self._fused_out is not None:
+                joined = ws.alloc((n.shape[0], self._fused_out.shape[1]), n.dtype)
+                outs = [stream.take_branch()]
+            else:
+                outs = [stream.take_branch() for _ in self.mixers]
             side = self._side_stream(proj.device) if len(self.mixers) > 1 and _PARALLEL_MIXERS else None
             main = torch.cuda.current_stream(proj.device)
             for i, (m, (c0, c1)) in enumerate(zip(self.mixers, self._fused_cols)):
+                def run(i=i, m=m, c0=c0, c1=c1):
+                    if joined is not None:
+                        k0, k1 = self._fused_out_cols[i]
+                        if not m.pre_output_into(proj[:, c0:c1], ctx, cache, joined[:, k0:k1], m.out_scale):
+                            raise RuntimeError("a mixer that joins output products declined to")
+                    else:
+                        m.forward_projected(proj[:, c0:c1], ctx, cache, outs[i])
                 if i == 0 and side is not None:
                     with branches.fork(main, side):
-                        m.forward_projected(proj[:, c0:c1], ctx, cache, outs[i])
+                        run()
                 else:
-                    m.forward_projected(proj[:, c0:c1], ctx, cache, outs[i])
+                    run()
             if side is not None:
                 main.wait_stream(side)
+            if joined is not None:
+                streaming.linear(joined, self._fused_out, outs[0], ctx)
         else:
             outs = []
             for m in self.mixers:
                 outs.append(stream.take_branch())
                 m.forward(n, ctx, cache, outs[-1])
-        results = [(out, m.out_scale) for m, out in zip(self.mixers, outs)]
+        if self._fused_in is not None and self._fused_out is not None:
+            results = [(outs[0], 1.0)]
+        else:
+            results = [(out, m.out_scale) for m, out in zip(self.mixers, outs)]
         if self.mixer_post_norm is not None:
             stream.add_normed(results, self.mixer_post_norm)
         else:

@@ -84,6 +84,22 @@ class GatedRotaryAttention(PagedSoftmaxAttention):
         self._make_split_counter(device)
 
     def forward_projected(self, proj: Tensor, ctx, cache, out: Tensor) -> None:
+        streaming.linear(self._gated_heads(proj, ctx, cache, None, 1.0), self.w_out, out, ctx)
+
+    def output_weight(self) -> Tensor:
+        return self.w_out
+
+    def joins_output_products(self) -> bool:
+        return self.has_gate
+
+    def pre_output_into(self, proj: Tensor, ctx, cache, into: Tensor, scale: float) -> bool:
+        if not self.has_gate:
+            return False
+        self._gated_heads(proj, ctx, cache, into, scale)
+        return True
+
+    def _gated_heads(self, proj: Tensor, ctx, cache, into: Optional[Tensor], scale: float) -> Tensor:
+        """The concatenated heads after the output gate (times ``scale``), [T, heads * vdim]."""
         T = proj.shape[0]
         ws = ctx.workspace
         kv = cache.paged(f"{self.name}.kv")
@@ -96,14 +112,14 @@ class GatedRotaryAttention(PagedSoftmaxAttention):
         attn = ws.alloc((T, H * Dp), proj.dtype)
         self._attend(q_rot, kv, ctx, attn)
         if self.has_gate:
-            gated = ws.alloc((T, self.o_dim), proj.dtype)
-            K.sigmoid_gate(attn, proj[:, c_g:c_g + self.o_dim], 1.0, gated, H, Dp, self.vdim)
+            gated = into if into is not None else ws.alloc((T, self.o_dim), proj.dtype)
+            K.sigmoid_gate(attn, proj[:, c_g:c_g + self.o_dim], scale, gated, H, Dp, self.vdim)
         elif Dp != self.vdim:
             gated = ws.alloc((T, self.o_dim), proj.dtype)
             gated.view(T, H, self.vdim).copy_(attn.view(T, H, Dp)[:, :, :self.vdim])
         else:
             gated = attn
-        streaming.linear(gated, self.w_out, out, ctx)
+        return gated
 
 
 register_mixer("rotary_gated_attention", GatedRotaryAttention)

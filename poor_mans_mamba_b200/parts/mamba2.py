@@ -22,7 +22,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..kernels import ops as K
-from . import branches
+from . import branches, streaming
 from .base import Mixer, ParamSpec, StateSpec, register_mixer
 
 Tensor = torch.Tensor
@@ -129,6 +129,7 @@ class Mamba2Mixer(Mixer):
         self.a_log = params["A_log"].contiguous()
         self.d_skip = params["D"].contiguous()
         self.norm_w = params["norm.weight"].contiguous() if self.gated_norm else None
+        self._scaled_norm_w: Dict[float, Tensor] = {}
         self.out_b = params["out_proj.bias"].contiguous() if self.proj_bias else None
         in_b = params["in_proj.bias"] if self.proj_bias else None
         dt_bias = params["dt_bias"]
@@ -167,7 +168,7 @@ class Mamba2Mixer(Mixer):
         self.forward_projected(proj, ctx, cache, out)
 
     def forward_projected(self, proj: Tensor, ctx, cache, out: Tensor) -> None:
-        K.linear(self.pre_output(proj, ctx, cache), self.w_out, out)
+        streaming.linear(self.pre_output(proj, ctx, cache), self.w_out, out, ctx)  # (few tokens: the weight-streaming product)
         if self.out_b is not None:
             K.add_row_bias_(out, self.out_b)
 
@@ -177,12 +178,22 @@ class Mamba2Mixer(Mixer):
     def output_bias(self) -> Optional[Tensor]:
         return self.out_b
 
+    def joins_output_products(self) -> bool:
+        return self.norm_w is not None and self.out_b is None
+
+    def pre_output_into(self, proj: Tensor, ctx, cache, into: Tensor, scale: float) -> bool:
+        if not self.joins_output_products():
+            return False
+        self.pre_output(proj, ctx, cache, into=into, scale=scale)
+        return True
+
     def accepts_length_bounds(self, dtype: torch.dtype, page_size: int) -> bool:
         # the tcgen05 scan's blocks find their chunk's sequence from the lengths on the device and
         # leave when there is none; the convolution and the lone tokens' scan go by token or sequence
         return _TC_SCAN and dtype == torch.bfloat16 and K.ssd_tc_supported(self.d_head, self.d_state)
 
-    def pre_output(self, proj: Tensor, ctx, cache) -> Tensor:
+    def pre_output(self, proj: Tensor, ctx, cache, into: Optional[Tensor] = None, scale: float = 1.0) -> Tensor:
+        """``into``/``scale`` (gated norm only): the result times ``scale`` goes into that column block."""
         T = proj.shape[0]
         ws = ctx.workspace
         i_dim = self.d_ssm
@@ -249,8 +260,13 @@ class Mamba2Mixer(Mixer):
             window_updating[0].wait_stream(window_updating[1])
         if gate is not None:
             return y
-        gated = ws.alloc((T, i_dim), proj.dtype)
-        K.gated_norm(y, z, self.z_scale, self.z_bias, self.norm_w, self.norm_eps, self.norm_groups,
+        gated = into if into is not None else ws.alloc((T, i_dim), proj.dtype)
+        norm_w = self.norm_w
+        if scale != 1.0:  # the scale rides in the norm's weight (made once per value)
+            norm_w = self._scaled_norm_w.get(scale)
+            if norm_w is None:
+                norm_w = self._scaled_norm_w[scale] = (self.norm_w * scale).contiguous()
+        K.gated_norm(y, z, self.z_scale, self.z_bias, norm_w, self.norm_eps, self.norm_groups,
                      self.norm_before_gate, gated)
         return gated
 

@@ -14,7 +14,7 @@ that the routed part of a step is a fixed chain of launches whatever the router 
 (the (token, choice) pairs sorted by expert, on the device), the grouped [gate | up] product with the
 activation in its epilogue, the grouped down product, and the weighted sum, which also adds the
 shared expert.  The router's weights and logits, the softmax and the weighted sum are float in both
-storage types.
+storage types; the experts' outputs wait for the sum in the storage type.
 """
 from __future__ import annotations
 
@@ -32,6 +32,7 @@ Tensor = torch.Tensor
 # The grouped products of steps with at least this many (token, choice) pairs run on tcgen05
 # (PMM_TCGEN05_MOE=0: the mma.sync form throughout).
 _TC_FROM_PAIRS = 1024
+_FEW_PAIRS = 256         # up to here an expert has a handful of rows: tiles of 16 rows, a deeper ring of K slices
 _TC_FROM_TILES = 96      # the shared expert's fused [gate | up] launch, as for the dense feed-forward
 _SIDE_SHARED = os.environ.get("PMM_SIDE_SHARED_EXPERT", "1") == "1"
 _TC_MOE = os.environ.get("PMM_TCGEN05_MOE", "1") == "1"
@@ -105,7 +106,7 @@ class RoutedGLU(FeedForward):
         tile_start = ws.alloc((E + 1,), torch.int32)
         perm = ws.alloc((A,), torch.int32)
         act = ws.alloc((A, F), x.dtype)
-        y = ws.alloc((A, D), torch.float32)
+        y = ws.alloc((A, D), x.dtype)
         # The shared expert only shares the input with the routed ones: it runs on a side stream beside their
         # chain of launches (a parallel branch of a recorded step) and is joined before the weighted sum.
         shared = side = None
@@ -120,7 +121,7 @@ class RoutedGLU(FeedForward):
                 self._shared(x, shared, ctx)
         # Steps of many tokens in bfloat16: tcgen05 tiles of 128 sorted rows (the token rows are gathered
         # into that order first).  Fewer pairs, or rows that are no whole 128-byte pieces: mma.sync tiles of
-        # 64 rows, which read the token rows through the plan.  Anything else (float32, rows that are no
+        # 64 rows (16 in steps of few pairs), which read the token rows through the plan.  Anything else (float32, rows that are no
         # multiple of 8 elements) runs in float on the CUDA cores.
         if (_TC_MOE and A >= _TC_FROM_PAIRS and K.moe_tc_supported(x, self.gate_up, F)
                 and K.moe_tc_supported(act, self.down, D)):
@@ -131,11 +132,13 @@ class RoutedGLU(FeedForward):
                           alpha=self.act_alpha, shift=self.act_shift)
             K.moe_tc_gemm(act, self.down, perm, offsets, tile_start, False, y)
         else:
-            mma = K.moe_gemm_tc_ok(x, self.gate_up) and K.moe_gemm_tc_ok(act, self.down)
-            K.moe_plan(ids, E, "mma" if mma else "float", offsets, tile_start, perm)
-            K.moe_gemm(x, self.gate_up, perm, offsets, tile_start, top, True, act, mma, limit=self.expert_limit,
+            form = "float"
+            if K.moe_gemm_tc_ok(x, self.gate_up) and K.moe_gemm_tc_ok(act, self.down):
+                form = "mma_few" if A <= _FEW_PAIRS else "mma"
+            K.moe_plan(ids, E, form, offsets, tile_start, perm)
+            K.moe_gemm(x, self.gate_up, perm, offsets, tile_start, top, True, act, form, limit=self.expert_limit,
                        alpha=self.act_alpha, shift=self.act_shift)
-            K.moe_gemm(act, self.down, perm, offsets, tile_start, top, False, y, mma)
+            K.moe_gemm(act, self.down, perm, offsets, tile_start, top, False, y, form)
         if side is not None:
             main.wait_stream(side)
         K.moe_combine(y, weights, shared, out)

@@ -203,7 +203,7 @@ def test_routed_experts_against_the_plain_sum(dtype, D, E, top, F, Fs, T, starve
     offsets = torch.empty(E + 1, dtype=torch.int32, device=DEV)
     tiles = torch.empty(E + 1, dtype=torch.int32, device=DEV)
     perm = torch.empty(T * top, dtype=torch.int32, device=DEV)
-    for tc in ("float", "mma", "tcgen05"):
+    for tc in ("float", "mma", "mma_few", "tcgen05"):
         K.moe_plan(ids, E, tc, offsets, tiles, perm)
         assert sorted(perm.cpu().tolist()) == list(range(T * top))
         flat, off, rows = ids.view(-1).cpu(), offsets.cpu().tolist(), K.moe_tile_rows(tc)
