@@ -15,9 +15,12 @@
 
 namespace pmm {
 
+constexpr int kRopeMaxPairs = 128;  // rot_dims <= 256
+
+// `sn`, `cs`: the token's sines and cosines per rotated pair (shared memory, made once a token).
 template <typename S>
 __device__ __forceinline__ float rotated(const S* __restrict__ head, const float* __restrict__ bias, int i, int rot_dims,
-                                         float pos, const float* __restrict__ inv_freq, int half_layout) {
+                                         const float* __restrict__ sn_t, const float* __restrict__ cs_t, int half_layout) {
   const float x = ldf(head + i) + (bias ? bias[i] : 0.f);
   if (i >= rot_dims) return x;
   const int half = rot_dims >> 1;
@@ -25,8 +28,7 @@ __device__ __forceinline__ float rotated(const S* __restrict__ head, const float
   const int j = half_layout ? (second ? i - half : i + half) : (i ^ 1);
   const int f = half_layout ? (second ? i - half : i) : (i >> 1);
   const float other = ldf(head + j) + (bias ? bias[j] : 0.f);
-  float sn, cs;
-  sincosf(pos * inv_freq[f], &sn, &cs);
+  const float sn = sn_t[f], cs = cs_t[f];
   return second ? x * cs + other * sn : x * cs - other * sn;
 }
 
@@ -39,11 +41,14 @@ __global__ void __launch_bounds__(256)
                             int page_size, S* __restrict__ q_out, int H, int G, int d, int dv, int Dp,
                             int rot_dims, int half_layout, const float* __restrict__ q_bias,
                             const float* __restrict__ k_bias, const float* __restrict__ v_bias) {
+  __shared__ float sn_t[kRopeMaxPairs], cs_t[kRopeMaxPairs];
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const float fpos = static_cast<float>(pos);
+  for (int f = threadIdx.x; f < rot_dims / 2; f += blockDim.x) sincosf(fpos * inv_freq[f], &sn_t[f], &cs_t[f]);
+  __syncthreads();
   const int n_q = H * Dp, n_kv = G * Dp;
   const int page = block_table[static_cast<size_t>(seq_of[t]) * max_blocks + pos / page_size];
   S* k_row = pool + (static_cast<size_t>(page) * 2 * page_size + pos % page_size) * n_kv;
@@ -52,12 +57,12 @@ __global__ void __launch_bounds__(256)
     if (e < n_q) {
       const int h = e / Dp, i = e - h * Dp;
       const float val = i < d ? rotated(q + static_cast<long long>(t) * ld_q + h * d, q_bias ? q_bias + h * d : nullptr, i, rot_dims,
-                                        fpos, inv_freq, half_layout) : 0.f;
+                                        sn_t, cs_t, half_layout) : 0.f;
       stf(q_out + static_cast<size_t>(t) * n_q + e, val);
     } else if (e < n_q + n_kv) {
       const int c = e - n_q, g = c / Dp, i = c - g * Dp;
       const float val = i < d ? rotated(k + static_cast<long long>(t) * ld_k + g * d, k_bias ? k_bias + g * d : nullptr, i, rot_dims,
-                                        fpos, inv_freq, half_layout) : 0.f;
+                                        sn_t, cs_t, half_layout) : 0.f;
       stf(k_row + c, val);
     } else {
       const int c = e - n_q - n_kv, g = c / Dp, i = c - g * Dp;
@@ -79,7 +84,7 @@ PMM_EXPORT int pmm_rope_pairs_store(const void* q, long long ld_q, const void* k
                                     cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || G <= 0 || d <= 0 || dv <= 0 || Dp < d || Dp < dv || rot_dims < 0 || rot_dims > d || rot_dims % 2 ||
-      (rot_dims > 0 && !inv_freq) || page_size <= 0)
+      rot_dims > 2 * pmm::kRopeMaxPairs || (rot_dims > 0 && !inv_freq) || page_size <= 0)
     return PMM_ERR_BAD_ARGUMENT;
   PMM_DISPATCH_DTYPE(dtype, S, pmm::launch_pdl(pmm::rope_pairs_store_kernel<S>, dim3(T), dim3(256), 0, stream,
                                                static_cast<const S*>(q), ld_q, static_cast<const S*>(k), ld_k,
