@@ -505,7 +505,7 @@ def tafesun_config(falcon, ff_sizes, layers):
     experts, top, expert_ff, shared_ff = ff_sizes
     hd = falcon["head_dim"]
     left = {"heads": falcon["num_attention_heads"], "kv_heads": falcon["num_key_value_heads"], "dim": hd, "vdim": hd,
-            "scale": hd ** -0.5, "rot": {"dims": hd // 2, "base": 1e6, "scaling": {"factor": 4.0}}}
+            "scale": hd ** -0.5, "rot": {"dims": hd // 2, "base": 5e5, "scaling": {"factor": 8.0}}}
     right = {"heads": falcon["mamba_n_heads"], "vdim": falcon["mamba_d_head"], "state": falcon["mamba_d_state"],
              "groups": falcon["mamba_n_groups"], "conv": falcon["mamba_d_conv"], "norm_groups": falcon["mamba_n_groups"]}
     mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff, "limit": 7.0},

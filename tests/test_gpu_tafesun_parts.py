@@ -69,7 +69,7 @@ def test_tanh_norm_with_the_residual_fold(dtype, D):
 # ----------------------------------------------------------------------------- rotation, biases, padded heads
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,d,dv,rot,factor", [(4, 2, 16, 24, 8, 2.0), (2, 1, 32, 16, 32, 8.0), (1, 1, 8, 40, 0, 1.0),
-                                                 (6, 3, 64, 128, 16, 4.0), (3, 3, 24, 8, 24, 1.0)])
+                                                 (8, 2, 64, 96, 48, 3.0), (3, 3, 24, 8, 24, 1.0)])
 def test_half_layout_rotation_into_the_pages(dtype, H, G, d, dv, rot, factor):
     """Positions up to 1,000 in two sequences whose pages are not in order; the rotated queries and what the
     pages hold afterwards against the plain rotation (values unrotated, heads padded with zeros)."""
@@ -163,7 +163,7 @@ def _routed_case(D, E, top, F, Fs, seed, T, starve=None):
     (72, 5, 2, 40, 56, 33, None),      # rows of whole 16-byte groups: the tensor-core products in bfloat16
     (100, 3, 3, 20, 0, 7, None),       # every expert for every token, no shared expert, float products
     (44, 9, 1, 12, 8, 300, 4),         # one expert a token, many tiles an expert, an expert without tokens
-    (64, 16, 4, 64, 128, 1, None),     # a single token
+    (64, 12, 5, 48, 80, 1, None),      # a single token
     (128, 8, 2, 96, 32, 517, 0),       # several row tiles, a ragged last one
     (256, 6, 3, 192, 64, 700, 2),      # rows of whole 128-byte pieces and many pairs: the tcgen05 products in bfloat16
     (128, 4, 1, 64, 0, 1500, None),    # the same with one expert a token
