@@ -196,7 +196,9 @@ def test_routed_experts_against_the_plain_sum(dtype, D, E, top, F, Fs, T, starve
     gap = torch.minimum(gap, val[:, -1] - rest.max(dim=-1).values) if top < E else gap
     sure = gap > 1e-3
     assert torch.equal(ids.cpu().long()[sure], idx[sure])
-    close(pw[sure.to(DEV)], torch.softmax(val, dim=-1)[sure], torch.float32, "router weights", f32=1e-5)
+    if bool(sure.any()):
+        close(pw[sure.to(DEV)], torch.softmax(val, dim=-1)[sure], torch.float32, "router weights", f32=1e-5)
+    assert T < 8 or int(sure.sum()) >= T // 2  # (most tokens are far from a close call)
     if starve is not None:
         assert not bool((ids == starve).any())
     # the plan: every pair once, grouped by expert
